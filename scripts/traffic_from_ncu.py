@@ -1,5 +1,5 @@
 #!/usr/bin/env python
-"""profiles/traffic.json from the per-case ncu captures (scripts/gpu_r02_profile.sh): DRAM bytes read + written per LAUNCH of
+"""profiles/traffic.json from the per-case ncu captures: DRAM bytes read + written per LAUNCH of
 the matvec kernel that carries the case (the launches with the most bytes: the same capture also sees the 1-layer decode
 leg of the bench command), the matvecs that launch carries (bytes / algorithmic bytes of one matvec, rounded) and the kernel."""
 import collections
