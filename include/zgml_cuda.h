@@ -49,8 +49,83 @@ typedef enum ZgOpTag {
     /* Extensions (no zgml counterpart: the reference has no distributed layer).  Emitted only by
      * the sharded session of this repo; need zg_cuda_comm_init().  One NCCL collective each, in program order. */
     ZG_OP_ALLREDUCE = 12, /* buf[offset .. offset + n) = sum over ranks, in place */
-    ZG_OP_ALLGATHER = 13  /* dst[dst_offset + r * n ..) = rank r's src[src_offset .. + n), every rank */
+    ZG_OP_ALLGATHER = 13, /* dst[dst_offset + r * n ..) = rank r's src[src_offset .. + n), every rank */
+    /* Sequence-model extensions (no zgml counterpart): the building blocks of decoder stacks that are not LLaMA-shaped —
+     * dense 16-bit / f32 weights, affine norms with a fused residual, windowed attention with a sink, short causal
+     * convolutions, a gated delta-rule recurrence, a routed mixture of experts.  All take a ZgSeqOp (below); per-sequence
+     * state (key ring, recurrent state, convolution tail) lives in EXTERNAL buffers shared by the programs of a session,
+     * and the run-time position / state slot / token ids are read from a small control buffer, so one CUDA graph serves
+     * every step. */
+    ZG_OP_EMBED = 14,
+    ZG_OP_LINEAR = 15,
+    ZG_OP_NORM = 16,
+    ZG_OP_WINDOW_ATTENTION = 17,
+    ZG_OP_CAUSAL_CONV = 18,
+    ZG_OP_DELTA_RULE = 19,
+    ZG_OP_ROUTE = 20,
+    ZG_OP_MOE_FFN = 21,
+    ZG_OP_END = 22
 } ZgOpTag;
+
+/* Parameter pack of the sequence-model ops.  buf[] are program buffer indices (ZG_NO_BUF: absent), off[] element offsets,
+ * n[] integers, f[] floats; buf[0] is always the destination.  Activations are f32.  A WEIGHT operand is (buffer, offset in
+ * weight elements) plus the op's `wdt`: ZG_W_F32 (the buffer holds floats) or ZG_W_BF16 (it holds bfloat16 bit patterns,
+ * two per f32 slot; widened exactly on load).  Linear weights are [out, in] row-major, applied as W x.  All arithmetic and
+ * accumulation is f32.
+ *
+ * Control buffer `ctl` (int32 words inside an f32 buffer, written by the host before every execution):
+ *   [0] position of the step's first token in its sequence, [1] state slot, [ZG_CTL_IDS ..) the step's token ids.
+ *
+ * EMBED             dst[t, :] = table[ids[t], :] * f0
+ *                   buf 0 dst 1 ctl 2 table | off 0 table | n 0 T 1 D 2 wdt | f 0 scale
+ * LINEAR            dst[m, n] = sum_k src[m, k] W[n, k] (+ bias[n])
+ *                   buf 0 dst 1 src 2 W 3 bias | off 0 W 1 bias 2 src 3 dst | n 0 M 1 N 2 K 3 src row stride 4 dst row stride 5 wdt
+ * NORM              dst = (res +) norm(src) * w ; kind 0: (x - mean) / sqrt(var + eps), kind 1: x / sqrt(mean(x^2) + eps)
+ *                   buf 0 dst 1 src 2 w 3 res | off 0 w | n 0 rows 1 cols 2 kind 3 wdt | f 0 eps
+ * WINDOW_ATTENTION  causal attention over the last `window` positions whose keys double as values (one projection, one cache),
+ *                   grouped query heads, scores capped smoothly (cap * tanh(s / cap), f1 = 0: off), a per-distance per-head
+ *                   additive bias table [window, H] (f32 program buffer), a softmax whose denominator carries an extra 1 (a
+ *                   sink with score 0 and no value), and an elementwise sigmoid gate on the heads' output.  The step's keys
+ *                   are first appended to a ring of R >= window - 1 + T positions per state slot (external buffer
+ *                   [slots, R, G * dim]; position p lives in row p mod R).
+ *                   buf 0 dst [T, H * dim] 1 proj (rows hold q | k | gate logits) 2 key ring 3 bias table 4 ctl
+ *                   off 0 q 1 k 2 gate (columns inside a proj row) | n 0 T 1 H 2 G 3 dim 4 proj row stride 5 window 6 R
+ *                   f 0 score scale 1 cap
+ * CAUSAL_CONV       per-channel FIR over time with carried inputs: dst[t, c] = act(sum_j w[c, j] x[t - (taps - 1) + j, c]), x
+ *                   before the step taken from the state (external [slots, taps - 1, C], zeros for a fresh slot), which is then
+ *                   advanced by the step's inputs.  act 0: none, 1: SiLU.
+ *                   buf 0 dst 1 src 2 w [C, taps] 3 state 4 ctl | off 0 w 1 src 2 dst | n 0 T 1 C 2 taps 3 src row stride
+ *                   4 dst row stride 5 act 6 wdt
+ * DELTA_RULE        gated delta rule with one decay per head and key channel, state S [dim, vdim] per head (external
+ *                   [slots, H, dim, vdim], f32): q, k -> unit vectors (x / sqrt(sum x^2 + f1)), q *= f2; beta = sigmoid(b);
+ *                   g = exp(-exp(A_log[h]) * softplus(a + dt_bias)); per token S <- g * S (rows), u = beta * (v - S^T k),
+ *                   S <- S + k u^T, o = S^T q; then o / sqrt(mean(o^2) + f0) * norm_w * sigmoid(gate).  Query / key head of
+ *                   head h is h / (H / G).
+ *                   buf 0 dst [T, H * vdim] 1 qkv 2 beta logits 3 a 4 gate logits 5 weights 6 state 7 ctl
+ *                   off 0 q 1 k 2 v (columns of a qkv row) 3 beta (column of its row) 4 A_log 5 dt_bias 6 norm_w (weights)
+ *                   n 0 T 1 H 2 G 3 dim 4 vdim 5 qkv row stride 6 beta row stride 7 a row stride 8 gate row stride 9 wdt
+ *                   f 0 output-norm eps 1 unit-vector eps 2 q scale
+ * ROUTE             s = softmax(logits) over all NE outputs; the `top` largest of s + correction are chosen (ties: lowest
+ *                   index); dst[t, c] = {index as int32 bits, s[index]} (weights not renormalised)
+ *                   buf 0 dst [T, top, 2] 1 logits 2 correction | off 0 correction 1 logits | n 0 T 1 NE 2 top 3 logits row
+ *                   stride 4 wdt
+ * MOE_FFN           dst[t] = sum_c weight_c * expert_{index_c}(src[t]); expert e < E: W_down (g * sigmoid(f1 * g) * (u + 1)),
+ *                   g = min(W_gate x, f0), u = clamp(W_up x, -f0, f0); index >= E: the identity (x itself).  Expert weights
+ *                   are stacked [E, ff, D] (gate, up) and [E, D, ff] (down).
+ *                   buf 0 dst 1 src 2 route 3 weights 4 scratch [T, top, ff] | off 0 gate 1 up 2 down | n 0 T 1 D 2 ff 3 E
+ *                   4 top 5 wdt | f 0 limit 1 alpha */
+#define ZG_NO_BUF 0xFFFFFFFFu
+#define ZG_W_F32 0
+#define ZG_W_BF16 1
+#define ZG_CTL_POS 0
+#define ZG_CTL_SLOT 1
+#define ZG_CTL_IDS 8
+typedef struct ZgSeqOp {
+    uint32_t buf[8];
+    uint32_t off[8];
+    uint32_t n[10];
+    float f[4];
+} ZgSeqOp;
 
 /* MatMulGeometry — reference src/backend.zig:146-158 (all usize). */
 typedef struct ZgMatMulGeometry {
@@ -113,6 +188,7 @@ typedef struct ZgOp {
         } fused_elementwise;
         struct { uint32_t buf, offset, n; } allreduce;
         struct { uint32_t dst, src, n, dst_offset, src_offset; } allgather;
+        ZgSeqOp seq;
     } u;
 } ZgOp;
 
@@ -144,6 +220,16 @@ typedef struct ZgQWeight {
  * time instead of holding every expanded i8 copy in host memory until compile (70B: 69.5 GB). */
 #define ZG_QWEIGHT_RESIDENT ((size_t)-1)
 
+/* Extension: a program buffer that lives OUTSIDE the program — caller-owned device memory (zg_cuda_malloc) that several
+ * programs of one session share: dense weights, per-sequence state.  The program neither zero-fills nor frees it;
+ * buffer_sizes[buf_idx] must equal `elems`. */
+typedef struct ZgExternBuffer {
+    uint32_t buf_idx;
+    uint32_t _pad;
+    void* device_ptr;   /* 16-byte aligned */
+    size_t elems;       /* f32 slots */
+} ZgExternBuffer;
+
 /* DeviceProgram — reference src/backend.zig:270-275. buffer_sizes in f32 elements. */
 typedef struct ZgProgram {
     const ZgOp* ops;
@@ -154,6 +240,8 @@ typedef struct ZgProgram {
     size_t n_uploads;
     const ZgQWeight* qweights;
     size_t n_qweights;
+    const ZgExternBuffer* externs;   /* extension; NULL / 0 for the reference's programs */
+    size_t n_externs;
 } ZgProgram;
 
 /* Subset of RuntimeProfile (reference src/profile.zig:819-842) that a CUDA

@@ -18,6 +18,12 @@ EW_NAMES = {"add": 7, "mul": 8, "neg": 9, "abs": 10, "sgn": 11, "step": 12, "rel
  OP_REPEAT, OP_SLICE_ASSIGN, OP_ROPE, OP_ATTENTION, OP_FUSED_ELEMENTWISE) = range(12)
 OP_COUNT = 12
 OP_ALLREDUCE, OP_ALLGATHER = 12, 13   # multi-GPU extensions (need comm_init)
+# sequence-model extensions (ZgSeqOp parameter packs)
+(OP_EMBED, OP_LINEAR, OP_NORM, OP_WINDOW_ATTENTION, OP_CAUSAL_CONV, OP_DELTA_RULE, OP_ROUTE, OP_MOE_FFN) = range(14, 22)
+OP_END = 22
+NO_BUF = 0xFFFFFFFF
+W_F32, W_BF16 = 0, 1
+CTL_POS, CTL_SLOT, CTL_IDS = 0, 1, 8
 QWEIGHT_RESIDENT = (1 << 64) - 1
 OP_TAG_NAMES = ["elementwise", "matmul", "qmatmul", "softmax", "layernorm", "rmsnorm", "reduce",
                 "repeat", "slice_assign", "rope", "attention", "fused_elementwise"]
@@ -100,12 +106,14 @@ class _AllGather(C.Structure):
     _fields_ = [(n, u32) for n in ("dst", "src", "n", "dst_offset", "src_offset")]
 
 
+class ZgSeqOp(C.Structure):
+    _fields_ = [("buf", u32 * 8), ("off", u32 * 8), ("n", u32 * 10), ("f", f32 * 4)]
 class _OpUnion(C.Union):
     _fields_ = [("elementwise", _Elementwise), ("matmul", _MatMul), ("qmatmul", _QMatMul),
                 ("softmax", _Softmax), ("layernorm", _Norm), ("rmsnorm", _Norm), ("reduce", _Reduce),
                 ("repeat", _Repeat), ("slice_assign", _SliceAssign), ("rope", _Rope),
                 ("attention", _Attention), ("fused_elementwise", _FusedElementwise),
-                ("allreduce", _AllReduce), ("allgather", _AllGather)]
+                ("allreduce", _AllReduce), ("allgather", _AllGather), ("seq", ZgSeqOp)]
 
 
 class ZgOp(C.Structure):
@@ -121,10 +129,12 @@ class ZgQWeight(C.Structure):
                 ("rows", sz), ("cols", sz), ("block_size", sz)]
 
 
+class ZgExternBuffer(C.Structure):
+    _fields_ = [("buf_idx", u32), ("_pad", u32), ("device_ptr", C.c_void_p), ("elems", sz)]
 class ZgProgram(C.Structure):
     _fields_ = [("ops", C.POINTER(ZgOp)), ("n_ops", sz), ("n_buffers", sz), ("buffer_sizes", C.POINTER(sz)),
                 ("initial_uploads", C.POINTER(ZgIO)), ("n_uploads", sz), ("qweights", C.POINTER(ZgQWeight)),
-                ("n_qweights", sz)]
+                ("n_qweights", sz), ("externs", C.POINTER(ZgExternBuffer)), ("n_externs", sz)]
 
 
 class ZgProfile(C.Structure):

@@ -190,6 +190,62 @@ class DeviceOp:
         return o
 
 
+    # Sequence-model extensions (ZgSeqOp parameter packs, include/zgml_cuda.h).  A weight operand is a
+    # (buffer, element offset) pair read as `wdt` (abi.W_F32 / abi.W_BF16).
+    @staticmethod
+    def _seq(tag, bufs, offs=(), ns=(), fs=()):
+        o = DeviceOp._mk(tag)
+        s = o.u.seq
+        for i in range(8):
+            s.buf[i] = abi.NO_BUF if i >= len(bufs) or bufs[i] is None else bufs[i]
+        for i, v in enumerate(offs):
+            s.off[i] = int(v)
+        for i, v in enumerate(ns):
+            s.n[i] = int(v)
+        for i, v in enumerate(fs):
+            s.f[i] = float(v)
+        return o
+
+    @staticmethod
+    def embed(dst, ctl, table, table_off, T, D, scale, wdt):
+        return DeviceOp._seq(abi.OP_EMBED, [dst, ctl, table], [table_off], [T, D, wdt], [scale])
+
+    @staticmethod
+    def linear(dst, src, w, w_off, M, N, K, wdt, bias=None, bias_off=0, src_off=0, dst_off=0, src_rs=0, dst_rs=0):
+        return DeviceOp._seq(abi.OP_LINEAR, [dst, src, w, bias], [w_off, bias_off, src_off, dst_off],
+                             [M, N, K, src_rs or K, dst_rs or N, wdt])
+
+    @staticmethod
+    def norm(dst, src, w, w_off, rows, cols, eps, wdt, kind="layer", res=None):
+        return DeviceOp._seq(abi.OP_NORM, [dst, src, w, res], [w_off], [rows, cols, {"layer": 0, "rms": 1}[kind], wdt], [eps])
+
+    @staticmethod
+    def window_attention(dst, proj, ring, bias_table, ctl, q_off, k_off, gate_off, T, H, G, dim, proj_rs, window, ring_rows, scale, cap):
+        return DeviceOp._seq(abi.OP_WINDOW_ATTENTION, [dst, proj, ring, bias_table, ctl], [q_off, k_off, gate_off],
+                             [T, H, G, dim, proj_rs, window, ring_rows], [scale, cap])
+
+    @staticmethod
+    def causal_conv(dst, src, w, w_off, state, ctl, T, C, taps, wdt, act="silu", src_off=0, dst_off=0, src_rs=0, dst_rs=0):
+        return DeviceOp._seq(abi.OP_CAUSAL_CONV, [dst, src, w, state, ctl], [w_off, src_off, dst_off],
+                             [T, C, taps, src_rs or C, dst_rs or C, {"none": 0, "silu": 1}[act], wdt])
+
+    @staticmethod
+    def delta_rule(dst, qkv, beta, a, gate, w, state, ctl, q_off, k_off, v_off, beta_off, a_log_off, dt_bias_off, norm_off,
+                   T, H, G, dim, vdim, qkv_rs, beta_rs, a_rs, gate_rs, wdt, norm_eps, unit_eps, q_scale):
+        return DeviceOp._seq(abi.OP_DELTA_RULE, [dst, qkv, beta, a, gate, w, state, ctl],
+                             [q_off, k_off, v_off, beta_off, a_log_off, dt_bias_off, norm_off],
+                             [T, H, G, dim, vdim, qkv_rs, beta_rs, a_rs, gate_rs, wdt], [norm_eps, unit_eps, q_scale])
+
+    @staticmethod
+    def route(dst, logits, w, corr_off, T, n_outputs, top, wdt, logits_off=0, logits_rs=0):
+        return DeviceOp._seq(abi.OP_ROUTE, [dst, logits, w], [corr_off, logits_off], [T, n_outputs, top, logits_rs or n_outputs, wdt])
+
+    @staticmethod
+    def moe_ffn(dst, src, route, w, scratch, gate_off, up_off, down_off, T, D, ff, experts, top, wdt, limit, alpha):
+        return DeviceOp._seq(abi.OP_MOE_FFN, [dst, src, route, w, scratch], [gate_off, up_off, down_off],
+                             [T, D, ff, experts, top, wdt], [limit, alpha])
+
+
 @dataclass
 class ProgramIO:  # reference src/backend.zig:252-257 (offset/size in bytes)
     buf_idx: int
@@ -245,12 +301,57 @@ class ResidentQuantizedWeight:
         return q
 
 
+class DeviceBuffer:
+    """Caller-owned device memory (zg_cuda_malloc) that programs reference as an external buffer: dense weights and
+    per-sequence state shared by the programs of one session.  `elems` counts f32 slots."""
+
+    def __init__(self, be: "CudaBackend", nbytes: int, zero: bool = True):
+        self.be = be
+        self.nbytes = (int(nbytes) + 15) & ~15
+        self.elems = self.nbytes // 4
+        self.ptr = be.lib.zg_cuda_malloc(be.ctx, self.nbytes)
+        if not self.ptr:
+            raise BackendError(f"device allocation of {self.nbytes} bytes failed: {last_error()}")
+        if zero:
+            self.fill_zero(0, self.nbytes)
+
+    def upload(self, host: np.ndarray, byte_offset: int = 0):
+        host = np.ascontiguousarray(host)
+        assert byte_offset + host.nbytes <= self.nbytes
+        if self.be.lib.zg_cuda_memcpy_h2d(self.be.ctx, self.ptr + byte_offset, host.ctypes.data, host.nbytes) != 0:
+            raise BackendError(f"upload failed: {last_error()}")
+
+    def download(self, dtype=np.float32, byte_offset: int = 0, count: Optional[int] = None) -> np.ndarray:
+        n = (self.nbytes - byte_offset) // np.dtype(dtype).itemsize if count is None else count
+        out = np.empty(n, dtype)
+        if self.be.lib.zg_cuda_memcpy_d2h(self.be.ctx, out.ctypes.data, self.ptr + byte_offset, out.nbytes) != 0:
+            raise BackendError(f"download failed: {last_error()}")
+        return out
+
+    def fill_zero(self, byte_offset: int, nbytes: int):
+        assert byte_offset + nbytes <= self.nbytes
+        if nbytes and self.be.lib.zg_cuda_memset(self.be.ctx, self.ptr + byte_offset, 0, nbytes) != 0:
+            raise BackendError(f"memset failed: {last_error()}")
+
+    def free(self):
+        if self.ptr:
+            self.be.lib.zg_cuda_free_device(self.be.ctx, self.ptr)
+            self.ptr = None
+
+
+@dataclass
+class ExternBuffer:  # ZgExternBuffer: program buffer `buf_idx` is the caller's `buffer`
+    buf_idx: int
+    buffer: DeviceBuffer
+
+
 @dataclass
 class DeviceProgram:  # reference src/backend.zig:270-275
     ops: List[abi.ZgOp]
     buffer_sizes: Sequence[int]
     initial_uploads: List[ProgramIO] = field(default_factory=list)
     qweights: List[QuantizedWeightUpload] = field(default_factory=list)
+    externs: List[ExternBuffer] = field(default_factory=list)
 
     @property
     def n_buffers(self) -> int:
@@ -279,6 +380,10 @@ class DeviceProgram:  # reference src/backend.zig:270-275
         p.buffer_sizes = C.cast(keep["sizes"], C.POINTER(C.c_size_t))
         p.initial_uploads, p.n_uploads = C.cast(keep["ups"], C.POINTER(abi.ZgIO)), len(self.initial_uploads)
         p.qweights, p.n_qweights = C.cast(keep["qws"], C.POINTER(abi.ZgQWeight)), len(self.qweights)
+        keep["ext"] = (abi.ZgExternBuffer * max(len(self.externs), 1))()
+        for i, e in enumerate(self.externs):
+            keep["ext"][i].buf_idx, keep["ext"][i].device_ptr, keep["ext"][i].elems = e.buf_idx, e.buffer.ptr, e.buffer.elems
+        p.externs, p.n_externs = C.cast(keep["ext"], C.POINTER(abi.ZgExternBuffer)), len(self.externs)
         return p, keep
 
 
@@ -390,6 +495,9 @@ class CudaBackend:
                         return False
             elif t in (abi.OP_ALLREDUCE, abi.OP_ALLGATHER):
                 pass   # world 1 (no comm_init): identity / local copy
+            elif abi.OP_EMBED <= t < abi.OP_END:
+                if any(b != abi.NO_BUF and b >= nb for b in op.u.seq.buf):
+                    return False
             elif t >= abi.OP_COUNT:
                 return False
         return True
@@ -422,6 +530,13 @@ class CudaBackend:
     def execute_program(self, handle: CompiledHandle, inputs: Sequence[ProgramIO], outputs: Sequence[ProgramIO]) -> None:
         ia, oa = _io_array(inputs), _io_array(outputs)
         self.lib.zg_cuda_execute(self.ctx, handle.ptr, ia, len(inputs), oa, len(outputs))
+
+    def read_buffer(self, handle: CompiledHandle, buf_idx: int, host: np.ndarray, elem_offset: int = 0) -> np.ndarray:
+        """Copy a program buffer (as the last execution left it) into `host`."""
+        ptr = self.lib.zg_cuda_program_buffer(handle.ptr, buf_idx)
+        if not ptr or self.lib.zg_cuda_memcpy_d2h(self.ctx, host.ctypes.data, ptr + 4 * elem_offset, host.nbytes) != 0:
+            raise BackendError(f"read_buffer({buf_idx}) failed: {last_error()}")
+        return host
 
     def free_program(self, handle: CompiledHandle) -> None:
         if handle.ptr:

@@ -59,6 +59,7 @@ struct ZgCudaProgram {
     std::vector<uint32_t> step_off;                // offset into d_steps per op
     std::vector<float*> buffers;
     std::vector<size_t> buffer_elems;
+    std::vector<bool> buffer_extern;   // caller-owned (ZgExternBuffer): shared with other programs, not freed with this one
     std::vector<ZgCudaQWeight*> qweights;
     std::vector<bool> qweight_owned;   // false: resident weight borrowed from the caller (ZG_QWEIGHT_RESIDENT)
     ZgDevStep* d_steps = nullptr;
@@ -231,7 +232,13 @@ static bool op_buffers_valid(const ZgOp& op, size_t nb) { // src/backend.zig:303
         }
         case ZG_OP_ALLREDUCE: return ok(op.u.allreduce.buf);
         case ZG_OP_ALLGATHER: return ok(op.u.allgather.dst) && ok(op.u.allgather.src);
-        default: return false;
+        default:
+            if (zg_is_seq_op(op.tag)) {
+                if (!ok(op.u.seq.buf[0])) return false;
+                for (int i = 1; i < 8; i++) if (op.u.seq.buf[i] != ZG_NO_BUF && !ok(op.u.seq.buf[i])) return false;
+                return true;
+            }
+            return false;
     }
 }
 
@@ -247,7 +254,8 @@ static void free_program(ZgCudaProgram* p) {
     cudaStreamSynchronize(p->ctx->stream);
     if (p->exec) cudaGraphExecDestroy(p->exec);
     if (p->graph) cudaGraphDestroy(p->graph);
-    for (float* b : p->buffers) cudaFree(b);
+    for (size_t i = 0; i < p->buffers.size(); i++)
+        if (i >= p->buffer_extern.size() || !p->buffer_extern[i]) cudaFree(p->buffers[i]);
     for (size_t i = 0; i < p->qweights.size(); i++)
         if (p->qweight_owned[i]) zg_cuda_qweight_free(p->ctx, p->qweights[i]);
     cudaFree(p->d_steps); cudaFree(p->d_dyn); cudaFree(p->d_batch); cudaFree(p->d_chain); cudaFree(p->d_attn_part); cudaFree(p->d_attn_cnt);
@@ -310,6 +318,10 @@ static bool validate_ops(const ZgCudaProgram* p, const ZgOp* ops, size_t n_ops) 
             if (w->K != q.K || w->N != q.N) { zg_set_error("op %zu: qweight is [%zu,%zu], op wants [%u,%u]", i, w->K, w->N, q.K, q.N); return false; }
         }
         if (ops[i].tag == ZG_OP_ATTENTION && ops[i].u.attention.d_head > 512) { zg_set_error("op %zu: d_head > 512", i); return false; }
+        if (zg_is_seq_op(ops[i].tag)) {
+            char why[96];
+            if (!zg_seq_op_valid(ops[i], p->buffer_elems.data(), p->buffers.size(), why, sizeof(why))) { zg_set_error("op %zu: %s", i, why); return false; }
+        }
     }
     return true;
 }
@@ -405,7 +417,13 @@ static void op_ranges(const ZgCudaProgram* p, const ZgOp& op, std::vector<ZgRang
             span(op.u.allgather.src, op.u.allgather.src_offset, op.u.allgather.n, false);
             span((uint32_t)p->buffers.size() + 1, 0, 1, true);
             break;
-        default: break;
+        default:
+            if (zg_is_seq_op(op.tag)) {   // whole buffers: these ops are few and large, finer ranges would buy no concurrency
+                const uint32_t wr = zg_seq_op_writes(op.tag);
+                for (int i = 0; i < 8; i++)
+                    if (op.u.seq.buf[i] != ZG_NO_BUF) whole(op.u.seq.buf[i], (wr >> i) & 1u);
+            }
+            break;
     }
 }
 
@@ -477,7 +495,18 @@ extern "C" ZgCudaProgram* zg_cuda_compile(ZgCudaCtx* ctx, const ZgProgram* prog)
     // buffers: max(size,1) f32, zero-filled (src/backend/reference.zig:89-93)
     p->buffers.assign(prog->n_buffers, nullptr);
     p->buffer_elems.assign(prog->n_buffers, 0);
+    p->buffer_extern.assign(prog->n_buffers, false);
+    for (size_t i = 0; i < prog->n_externs; i++) {   // caller-owned memory shared between programs: neither filled nor freed here
+        const ZgExternBuffer& e = prog->externs[i];
+        if (e.buf_idx >= prog->n_buffers || !e.device_ptr || (((size_t)e.device_ptr) & 15) || e.elems == 0 || e.elems != prog->buffer_sizes[e.buf_idx] ||
+            p->buffer_extern[e.buf_idx]) {
+            zg_set_error("compile: external buffer %zu is null, misaligned, repeated or not the declared size", i);
+            free_program(p); return nullptr;
+        }
+        p->buffers[e.buf_idx] = (float*)e.device_ptr; p->buffer_elems[e.buf_idx] = e.elems; p->buffer_extern[e.buf_idx] = true;
+    }
     for (size_t i = 0; i < prog->n_buffers; i++) {
+        if (p->buffer_extern[i]) continue;
         size_t n = prog->buffer_sizes[i] > 1 ? prog->buffer_sizes[i] : 1;
         size_t bytes = (n * sizeof(float) + 15) & ~(size_t)15;
         if (cudaMalloc(&p->buffers[i], bytes) != cudaSuccess) {
@@ -1689,6 +1718,7 @@ static bool launch_one(ZgCudaProgram* p, size_t i, cudaStream_t st) {
         }
     }
     if (zg_op_is_batched(op.tag)) return zg_launch_batch(op, p->d_batch + p->single_entry[i], 1, p->d_dyn, st);
+    if (zg_is_seq_op(op.tag)) return zg_launch_seq_op(ctx, op, p->buffers.data(), st);
     return zg_launch_op(ctx, op, p->buffers.data(), p->d_dyn, (uint32_t)i, p->d_steps + p->step_off[i], st);
 }
 

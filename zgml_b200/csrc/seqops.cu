@@ -1,0 +1,685 @@
+// Sequence-model DeviceOps (ZG_OP_EMBED .. ZG_OP_MOE_FFN, parameter packs documented in include/zgml_cuda.h): dense
+// 16-bit / f32 weights against f32 activations, affine norms with a fused residual, windowed attention with a sink over a
+// key ring, short causal convolutions with a carried tail, the gated delta-rule recurrence with per-channel decay, and a
+// routed mixture of experts.  Everything is accumulated in f32; a bfloat16 weight is widened exactly on load, so the two
+// weight formats differ only in bytes streamed.
+//
+// Per-sequence state lives in external program buffers indexed by the state slot of the control buffer; the position of
+// the step's first token comes from the same place, so a captured graph replays unchanged from step to step.
+#include "zg_internal.cuh"
+
+#include <cuda_bf16.h>
+
+namespace {
+
+typedef __nv_bfloat16 bf16;
+
+template <typename WT> __device__ __forceinline__ float wld(const WT* w, size_t i);
+template <> __device__ __forceinline__ float wld<float>(const float* w, size_t i) { return w[i]; }
+template <> __device__ __forceinline__ float wld<bf16>(const bf16* w, size_t i) { return __bfloat162float(w[i]); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+// sum over the whole block, result in every thread; sh: 32 floats
+__device__ float block_sum(float v, float* sh) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) sh[warp] = v;
+    __syncthreads();
+    float r = 0.0f;
+    for (int i = 0; i < nw; i++) r += sh[i];
+    return r;
+}
+__device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf(-z)); }
+__device__ __forceinline__ float softplusf_(float z) { return z > 20.0f ? z : log1pf(expf(z)); }
+__device__ __forceinline__ int ctl_word(const float* ctl, int i) { return reinterpret_cast<const int*>(ctl)[i]; }
+
+// ── EMBED ─────────────────────────────────────────────────────────────────────────────────────────────────────────
+template <typename WT>
+__global__ void k_embed(float* __restrict__ dst, const float* __restrict__ ctl, const WT* __restrict__ table, uint32_t D, float scale) {
+    const uint32_t t = blockIdx.x;
+    const size_t row = (size_t)ctl_word(ctl, ZG_CTL_IDS + t) * D;
+    for (uint32_t c = threadIdx.x; c < D; c += blockDim.x) dst[(size_t)t * D + c] = wld(table, row + c) * scale;
+}
+
+// ── LINEAR, few rows (decode): one warp per output feature, the weight row streamed once for all rows ─────────────────
+constexpr int kGemvRows = 8;
+template <typename WT>
+__global__ void k_linear_rows(float* __restrict__ dst, const float* __restrict__ src, const WT* __restrict__ W, const WT* __restrict__ bias,
+                              uint32_t M, uint32_t N, uint32_t K, uint32_t src_rs, uint32_t dst_rs) {
+    const uint32_t n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (n >= N) return;
+    const WT* w = W + (size_t)n * K;
+    float acc[kGemvRows];
+#pragma unroll
+    for (int m = 0; m < kGemvRows; m++) acc[m] = 0.0f;
+    for (uint32_t k = lane; k < K; k += 32) {
+        const float wv = wld(w, k);
+#pragma unroll
+        for (int m = 0; m < kGemvRows; m++)
+            if (m < (int)M) acc[m] = fmaf(src[(size_t)m * src_rs + k], wv, acc[m]);
+    }
+    const float b = bias ? wld(bias, n) : 0.0f;
+#pragma unroll
+    for (int m = 0; m < kGemvRows; m++) {
+        if (m < (int)M) {
+            const float s = warp_sum(acc[m]);
+            if (lane == 0) dst[(size_t)m * dst_rs + n] = s + b;
+        }
+    }
+}
+// 16-byte weight loads (8 bf16 / 4 f32 per lane and trip) when the row start and K allow it
+template <typename WT> struct WVec;
+template <> struct WVec<bf16> { static constexpr int n = 8; };
+template <> struct WVec<float> { static constexpr int n = 4; };
+template <typename WT>
+__device__ __forceinline__ void wld_vec(const WT* p, float* out);
+template <> __device__ __forceinline__ void wld_vec<bf16>(const bf16* p, float* out) {
+    const uint4 v = *reinterpret_cast<const uint4*>(p);
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) { out[2 * i] = __uint_as_float(u[i] << 16); out[2 * i + 1] = __uint_as_float(u[i] & 0xFFFF0000u); }
+}
+template <> __device__ __forceinline__ void wld_vec<float>(const float* p, float* out) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
+}
+template <typename WT, int MR>
+__global__ void k_linear_rows_vec(float* __restrict__ dst, const float* __restrict__ src, const WT* __restrict__ W, const WT* __restrict__ bias,
+                                  uint32_t M, uint32_t N, uint32_t K, uint32_t src_rs, uint32_t dst_rs) {
+    constexpr int V = WVec<WT>::n;
+    const uint32_t n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (n >= N) return;
+    const WT* w = W + (size_t)n * K;
+    float acc[MR];
+#pragma unroll
+    for (int m = 0; m < MR; m++) acc[m] = 0.0f;
+    for (uint32_t k = lane * V; k < K; k += 32 * V) {
+        float wv[V];
+        wld_vec<WT>(w + k, wv);
+#pragma unroll
+        for (int m = 0; m < MR; m++) {
+            if (m < (int)M) {
+                const float* x = src + (size_t)m * src_rs + k;
+#pragma unroll
+                for (int i = 0; i < V; i++) acc[m] = fmaf(x[i], wv[i], acc[m]);
+            }
+        }
+    }
+    const float b = bias ? wld(bias, n) : 0.0f;
+#pragma unroll
+    for (int m = 0; m < MR; m++) {
+        if (m < (int)M) {
+            const float s = warp_sum(acc[m]);
+            if (lane == 0) dst[(size_t)m * dst_rs + n] = s + b;
+        }
+    }
+}
+
+// ── LINEAR, many rows (prefill), exact f32: 64 x 64 tile, 16-deep k slices, 4 x 4 outputs per thread ──────────────────
+constexpr int kTM = 64, kTN = 64, kTK = 16;
+template <typename WT>
+__global__ void __launch_bounds__(256) k_linear_tile(float* __restrict__ dst, const float* __restrict__ src, const WT* __restrict__ W,
+                                                     const WT* __restrict__ bias, uint32_t M, uint32_t N, uint32_t K, uint32_t src_rs,
+                                                     uint32_t dst_rs) {
+    __shared__ float As[kTK][kTM + 4];
+    __shared__ float Ws[kTK][kTN + 4];
+    const uint32_t m0 = blockIdx.y * kTM, n0 = blockIdx.x * kTN;
+    const uint32_t tx = threadIdx.x & 15, ty = threadIdx.x >> 4;   // outputs: rows ty * 4 + i, columns tx * 4 + j
+    float acc[4][4] = {};
+    for (uint32_t k0 = 0; k0 < K; k0 += kTK) {
+        for (uint32_t e = threadIdx.x; e < kTM * kTK; e += 256) {
+            const uint32_t r = e / kTK, kk = e % kTK;
+            const uint32_t m = m0 + r, k = k0 + kk;
+            As[kk][r] = (m < M && k < K) ? src[(size_t)m * src_rs + k] : 0.0f;
+            const uint32_t n = n0 + r;
+            Ws[kk][r] = (n < N && k < K) ? wld(W, (size_t)n * K + k) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < kTK; kk++) {
+            float a[4], b[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) { a[i] = As[kk][ty * 4 + i]; b[i] = Ws[kk][tx * 4 + i]; }
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const uint32_t m = m0 + ty * 4 + i;
+        if (m >= M) continue;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const uint32_t n = n0 + tx * 4 + j;
+            if (n < N) dst[(size_t)m * dst_rs + n] = acc[i][j] + (bias ? wld(bias, n) : 0.0f);
+        }
+    }
+}
+
+// ── NORM: one CTA per row ────────────────────────────────────────────────────────────────────────────────────────
+template <typename WT>
+__global__ void k_norm(float* __restrict__ dst, const float* __restrict__ src, const WT* __restrict__ w, const float* __restrict__ res,
+                       uint32_t cols, uint32_t kind, float eps) {
+    __shared__ float sh[32];
+    const size_t row = (size_t)blockIdx.x * cols;
+    const float* x = src + row;
+    float mean = 0.0f;
+    if (kind == 0) {
+        float s = 0.0f;
+        for (uint32_t c = threadIdx.x; c < cols; c += blockDim.x) s += x[c];
+        mean = block_sum(s, sh) / (float)cols;
+    }
+    float q = 0.0f;
+    for (uint32_t c = threadIdx.x; c < cols; c += blockDim.x) { const float d = x[c] - mean; q = fmaf(d, d, q); }
+    const float inv = 1.0f / sqrtf(block_sum(q, sh) / (float)cols + eps);
+    for (uint32_t c = threadIdx.x; c < cols; c += blockDim.x) {
+        const float y = (x[c] - mean) * inv * wld(w, c);
+        dst[row + c] = res ? res[row + c] + y : y;
+    }
+}
+
+// ── WINDOW_ATTENTION ─────────────────────────────────────────────────────────────────────────────────────────────
+__global__ void k_ring_append(float* __restrict__ ring, const float* __restrict__ proj, const float* __restrict__ ctl, uint32_t k_off,
+                              uint32_t proj_rs, uint32_t width, uint32_t R) {
+    const uint32_t t = blockIdx.x;
+    const uint32_t pos = (uint32_t)ctl_word(ctl, ZG_CTL_POS) + t, slot = (uint32_t)ctl_word(ctl, ZG_CTL_SLOT);
+    float* row = ring + ((size_t)slot * R + pos % R) * width;
+    const float* k = proj + (size_t)t * proj_rs + k_off;
+    for (uint32_t c = threadIdx.x; c < width; c += blockDim.x) row[c] = k[c];
+}
+constexpr int kAttnMaxDim = 256;   // 8 channels per lane
+// one warp per (token, head): 32 keys at a time, lane = key for the scores, lane = channel for the weighted sum
+__global__ void k_window_attention(float* __restrict__ dst, const float* __restrict__ proj, const float* __restrict__ ring,
+                                   const float* __restrict__ bias, const float* __restrict__ ctl, uint32_t T, uint32_t H, uint32_t G,
+                                   uint32_t dim, uint32_t proj_rs, uint32_t q_off, uint32_t g_off, uint32_t window, uint32_t R,
+                                   float scale, float cap) {
+    extern __shared__ float sq[];                      // [warps][dim]
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    const uint32_t item = blockIdx.x * nw + warp;
+    if (item >= T * H) return;
+    const uint32_t t = item / H, h = item % H, kv = h / (H / G);
+    const uint32_t pos0 = (uint32_t)ctl_word(ctl, ZG_CTL_POS), slot = (uint32_t)ctl_word(ctl, ZG_CTL_SLOT);
+    const uint32_t p = pos0 + t;
+    const uint32_t lo = p + 1 >= window ? p + 1 - window : 0;
+    float* q = sq + warp * dim;
+    const float* qrow = proj + (size_t)t * proj_rs + q_off + (size_t)h * dim;
+    for (uint32_t c = lane; c < dim; c += 32) q[c] = qrow[c];
+    __syncwarp();
+    const size_t width = (size_t)G * dim;
+    const float* base = ring + (size_t)slot * R * width + (size_t)kv * dim;
+    float m = 0.0f, l = 1.0f;                          // the sink: score 0, weight exp(0 - m), no value
+    float acc[kAttnMaxDim / 32];
+#pragma unroll
+    for (int i = 0; i < kAttnMaxDim / 32; i++) acc[i] = 0.0f;
+    for (uint32_t j0 = lo; j0 <= p; j0 += 32) {
+        const uint32_t j = j0 + lane;
+        float s = -INFINITY;
+        if (j <= p) {
+            const float* k = base + (size_t)(j % R) * width;
+            float d = 0.0f;
+            for (uint32_t c = 0; c < dim; c++) d = fmaf(q[c], k[c], d);
+            s = d * scale;
+            if (cap > 0.0f) s = cap * tanhf(s / cap);
+            s += bias[(size_t)(p - j) * H + h];
+        }
+        const float m_new = fmaxf(m, warp_max(s));
+        const float corr = expf(m - m_new);
+        const float e = j <= p ? expf(s - m_new) : 0.0f;
+        l = l * corr + warp_sum(e);
+        m = m_new;
+        const uint32_t cnt = min(32u, p - j0 + 1);
+#pragma unroll
+        for (int i = 0; i < kAttnMaxDim / 32; i++) acc[i] *= corr;
+        for (uint32_t jj = 0; jj < cnt; jj++) {
+            const float pj = __shfl_sync(0xffffffffu, e, jj);
+            const float* k = base + (size_t)((j0 + jj) % R) * width;
+#pragma unroll
+            for (int i = 0; i < kAttnMaxDim / 32; i++) {
+                const uint32_t c = lane + 32 * i;
+                if (c < dim) acc[i] = fmaf(pj, k[c], acc[i]);
+            }
+        }
+    }
+    const float inv = 1.0f / l;
+    const float* grow = proj + (size_t)t * proj_rs + g_off + (size_t)h * dim;
+    float* out = dst + ((size_t)t * H + h) * dim;
+#pragma unroll
+    for (int i = 0; i < kAttnMaxDim / 32; i++) {
+        const uint32_t c = lane + 32 * i;
+        if (c < dim) out[c] = acc[i] * inv * sigmoidf_(grow[c]);
+    }
+}
+
+// ── CAUSAL_CONV ──────────────────────────────────────────────────────────────────────────────────────────────────
+template <typename WT>
+__global__ void k_causal_conv(float* __restrict__ dst, const float* __restrict__ src, const WT* __restrict__ w, const float* __restrict__ state,
+                              const float* __restrict__ ctl, uint32_t T, uint32_t C, uint32_t taps, uint32_t src_rs, uint32_t dst_rs, uint32_t act) {
+    const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= (size_t)T * C) return;
+    const uint32_t t = (uint32_t)(e / C), c = (uint32_t)(e % C);
+    const float* st = state + (size_t)ctl_word(ctl, ZG_CTL_SLOT) * (taps - 1) * C;
+    float y = 0.0f;
+    for (uint32_t j = 0; j < taps; j++) {
+        const int tau = (int)t - (int)(taps - 1) + (int)j;     // time relative to the step's first token
+        const float x = tau >= 0 ? src[(size_t)tau * src_rs + c] : st[(size_t)(tau + (int)(taps - 1)) * C + c];
+        y = fmaf(wld(w, (size_t)c * taps + j), x, y);
+    }
+    if (act == 1) y = y * sigmoidf_(y);
+    dst[(size_t)t * dst_rs + c] = y;
+}
+// state row r holds the input of time (first token of the NEXT step) - (taps - 1) + r; rows ascend, so shifting in place is safe
+__global__ void k_conv_advance(float* __restrict__ state, const float* __restrict__ src, const float* __restrict__ ctl, uint32_t T, uint32_t C,
+                               uint32_t taps, uint32_t src_rs) {
+    const uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    float* st = state + (size_t)ctl_word(ctl, ZG_CTL_SLOT) * (taps - 1) * C;
+    for (uint32_t r = 0; r + 1 < taps; r++) {
+        const int tau = (int)T - (int)(taps - 1) + (int)r;
+        st[(size_t)r * C + c] = tau >= 0 ? src[(size_t)tau * src_rs + c] : st[(size_t)(r + T) * C + c];
+    }
+}
+
+// ── DELTA_RULE ───────────────────────────────────────────────────────────────────────────────────────────────────
+// Columns of the state evolve independently given the token's k, q, decay and beta, so a head is split by value columns
+// over CTAs.  A thread keeps kDeltaRows consecutive key rows of one column in registers; the RS threads of a column sit in
+// adjacent lanes and meet by shuffles.  The per-token vectors (unit k, scaled unit q, decay) of kDeltaTile tokens are
+// prepared by the whole CTA at once, then the tokens are walked without further barriers.
+constexpr int kDeltaRows = 16, kDeltaTile = 8, kDeltaThreads = 128;
+template <typename WT>
+__global__ void __launch_bounds__(kDeltaThreads) k_delta_rule(
+    float* __restrict__ dst, const float* __restrict__ qkv, const float* __restrict__ betab, const float* __restrict__ ab, const WT* __restrict__ wts,
+    float* __restrict__ state, const float* __restrict__ ctl, uint32_t T, uint32_t H, uint32_t G, uint32_t dim, uint32_t vdim, uint32_t RS,
+    uint32_t q_off, uint32_t k_off, uint32_t v_off, uint32_t beta_off, uint32_t A_off, uint32_t dt_off, uint32_t qkv_rs, uint32_t beta_rs,
+    uint32_t a_rs, float unit_eps, float q_scale) {
+    extern __shared__ float sm[];
+    const uint32_t dpad = RS * kDeltaRows;             // rows incl. padding (k = q = 0, decay = 1 there)
+    float* sk = sm;                                    // [tile][dpad]
+    float* sq = sk + kDeltaTile * dpad;
+    float* sg = sq + kDeltaTile * dpad;
+    float* sbeta = sg + kDeltaTile * dpad;             // [tile]
+    const uint32_t h = blockIdx.y, kv = h / (H / G);
+    const uint32_t cols_per_cta = kDeltaThreads / RS;
+    const uint32_t r = threadIdx.x % RS, col = blockIdx.x * cols_per_cta + threadIdx.x / RS;
+    const bool live = col < vdim;
+    const uint32_t slot = (uint32_t)ctl_word(ctl, ZG_CTL_SLOT);
+    float* S_g = state + (((size_t)slot * H + h) * dim) * vdim;
+    float S[kDeltaRows];
+#pragma unroll
+    for (int i = 0; i < kDeltaRows; i++) {
+        const uint32_t row = r * kDeltaRows + i;
+        S[i] = (live && row < dim) ? S_g[(size_t)row * vdim + col] : 0.0f;
+    }
+    const float Ah = expf(wld(wts, (size_t)A_off + h));
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (uint32_t t0 = 0; t0 < T; t0 += kDeltaTile) {
+        const uint32_t nt = min((uint32_t)kDeltaTile, T - t0);
+        __syncthreads();
+        // prepare: warp w takes tokens w, w + 4, ...
+        for (uint32_t tt = warp; tt < nt; tt += kDeltaThreads / 32) {
+            const uint32_t t = t0 + tt;
+            const float* qr = qkv + (size_t)t * qkv_rs + q_off + (size_t)kv * dim;
+            const float* kr = qkv + (size_t)t * qkv_rs + k_off + (size_t)kv * dim;
+            const float* ar = ab + (size_t)t * a_rs + (size_t)h * dim;
+            float qq = 0.0f, kk = 0.0f;
+            for (uint32_t c = lane; c < dim; c += 32) { qq = fmaf(qr[c], qr[c], qq); kk = fmaf(kr[c], kr[c], kk); }
+            const float qn = q_scale / sqrtf(warp_sum(qq) + unit_eps), kn = 1.0f / sqrtf(warp_sum(kk) + unit_eps);
+            for (uint32_t c = lane; c < dpad; c += 32) {
+                const bool in = c < dim;
+                sk[tt * dpad + c] = in ? kr[c] * kn : 0.0f;
+                sq[tt * dpad + c] = in ? qr[c] * qn : 0.0f;
+                sg[tt * dpad + c] = in ? expf(-Ah * softplusf_(ar[c] + wld(wts, (size_t)dt_off + (size_t)h * dim + c))) : 1.0f;
+            }
+            if (lane == 0) sbeta[tt] = sigmoidf_(betab[(size_t)t * beta_rs + beta_off + h]);
+        }
+        __syncthreads();
+        for (uint32_t tt = 0; tt < nt; tt++) {
+            const uint32_t t = t0 + tt;
+            const float* k = sk + tt * dpad + r * kDeltaRows;
+            const float* q = sq + tt * dpad + r * kDeltaRows;
+            const float* g = sg + tt * dpad + r * kDeltaRows;
+            const float v = live ? qkv[(size_t)t * qkv_rs + v_off + (size_t)h * vdim + col] : 0.0f;
+            float ks = 0.0f;
+#pragma unroll
+            for (int i = 0; i < kDeltaRows; i++) { S[i] *= g[i]; ks = fmaf(S[i], k[i], ks); }
+            for (uint32_t o = 1; o < RS; o <<= 1) ks += __shfl_xor_sync(0xffffffffu, ks, o);
+            const float u = sbeta[tt] * (v - ks);
+            float os = 0.0f;
+#pragma unroll
+            for (int i = 0; i < kDeltaRows; i++) { S[i] = fmaf(k[i], u, S[i]); os = fmaf(S[i], q[i], os); }
+            for (uint32_t o = 1; o < RS; o <<= 1) os += __shfl_xor_sync(0xffffffffu, os, o);
+            if (live && r == 0) dst[((size_t)t * H + h) * vdim + col] = os;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < kDeltaRows; i++) {
+        const uint32_t row = r * kDeltaRows + i;
+        if (live && row < dim) S_g[(size_t)row * vdim + col] = S[i];
+    }
+}
+// o / rms(o) * norm_w * sigmoid(gate), one warp per (token, head), in place
+template <typename WT>
+__global__ void k_delta_out(float* __restrict__ dst, const float* __restrict__ gate, const WT* __restrict__ wts, uint32_t TH, uint32_t H,
+                            uint32_t vdim, uint32_t gate_rs, uint32_t nw_off, float eps) {
+    const uint32_t item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (item >= TH) return;
+    const uint32_t t = item / H, h = item % H;
+    float* o = dst + (size_t)item * vdim;
+    const float* g = gate + (size_t)t * gate_rs + (size_t)h * vdim;
+    float q = 0.0f;
+    for (uint32_t c = lane; c < vdim; c += 32) q = fmaf(o[c], o[c], q);
+    const float inv = 1.0f / sqrtf(warp_sum(q) / (float)vdim + eps);
+    for (uint32_t c = lane; c < vdim; c += 32) o[c] = o[c] * inv * wld(wts, (size_t)nw_off + c) * sigmoidf_(g[c]);
+}
+
+// ── ROUTE: one warp per token ────────────────────────────────────────────────────────────────────────────────────
+template <typename WT>
+__global__ void k_route(float* __restrict__ dst, const float* __restrict__ logits, const WT* __restrict__ corr, uint32_t T, uint32_t NE, uint32_t top,
+                        uint32_t logits_rs) {
+    extern __shared__ float sm[];                      // [warps][NE] choice scores
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t t = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (t >= T) return;
+    const float* z = logits + (size_t)t * logits_rs;
+    float* ch = sm + warp * NE;
+    float mx = -INFINITY;
+    for (uint32_t e = lane; e < NE; e += 32) mx = fmaxf(mx, z[e]);
+    mx = warp_max(mx);
+    float sum = 0.0f;
+    for (uint32_t e = lane; e < NE; e += 32) sum += expf(z[e] - mx);
+    const float inv = 1.0f / warp_sum(sum);
+    for (uint32_t e = lane; e < NE; e += 32) ch[e] = expf(z[e] - mx) * inv + wld(corr, e);
+    __syncwarp();
+    for (uint32_t c = 0; c < top; c++) {
+        float best = -INFINITY; uint32_t bi = 0xFFFFFFFFu;
+        for (uint32_t e = lane; e < NE; e += 32) if (ch[e] > best) { best = ch[e]; bi = e; }
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+        }
+        if (lane == 0) {
+            float* out = dst + ((size_t)t * top + c) * 2;
+            reinterpret_cast<int*>(out)[0] = (int)bi;
+            out[1] = bi < NE ? expf(z[bi] - mx) * inv : 0.0f;
+            if (bi < NE) ch[bi] = -INFINITY;
+        }
+        __syncwarp();
+    }
+}
+
+// dot of one weight row with an f32 vector by a whole warp (every lane gets the sum); 16-byte weight loads when aligned
+template <typename WT>
+__device__ __forceinline__ float warp_dot(const WT* __restrict__ w, const float* __restrict__ x, uint32_t K, uint32_t lane) {
+    constexpr int V = WVec<WT>::n;
+    float acc = 0.0f;
+    if (K % V == 0 && (reinterpret_cast<size_t>(w) & 15) == 0) {
+        for (uint32_t k = lane * V; k < K; k += 32 * V) {
+            float wv[V];
+            wld_vec<WT>(w + k, wv);
+#pragma unroll
+            for (int i = 0; i < V; i++) acc = fmaf(x[k + i], wv[i], acc);
+        }
+    } else {
+        for (uint32_t k = lane; k < K; k += 32) acc = fmaf(x[k], wld(w, k), acc);
+    }
+    return warp_sum(acc);
+}
+
+// ── MOE_FFN, token-wise form: every (token, choice) pair streams the rows of its expert (decode and short steps) ────────
+template <typename WT>
+__global__ void k_moe_up(float* __restrict__ y, const float* __restrict__ src, const float* __restrict__ route, const WT* __restrict__ wg,
+                         const WT* __restrict__ wu, uint32_t D, uint32_t ff, uint32_t E, uint32_t top, float limit, float alpha) {
+    const uint32_t pair = blockIdx.y;                  // token * top + choice
+    const uint32_t f = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    const uint32_t e = (uint32_t)reinterpret_cast<const int*>(route)[2 * (size_t)pair];
+    if (f >= ff || e >= E) return;                     // identity experts have no weights
+    const float* x = src + (size_t)(pair / top) * D;
+    const size_t row = ((size_t)e * ff + f) * D;
+    float g = warp_dot(wg + row, x, D, lane), u = warp_dot(wu + row, x, D, lane);
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    if (lane == 0) y[(size_t)pair * ff + f] = g * sigmoidf_(alpha * g) * (u + 1.0f);
+}
+template <typename WT>
+__global__ void k_moe_down(float* __restrict__ dst, const float* __restrict__ src, const float* __restrict__ y, const float* __restrict__ route,
+                           const WT* __restrict__ wd, uint32_t D, uint32_t ff, uint32_t E, uint32_t top) {
+    const uint32_t t = blockIdx.y;
+    const uint32_t d = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (d >= D) return;
+    float acc = 0.0f;
+    for (uint32_t c = 0; c < top; c++) {               // fixed order: the result does not depend on the launch shape
+        const size_t pair = (size_t)t * top + c;
+        const uint32_t e = (uint32_t)reinterpret_cast<const int*>(route)[2 * pair];
+        const float w = route[2 * pair + 1];
+        const float v = e < E ? warp_dot(wd + ((size_t)e * D + d) * ff, y + pair * ff, ff, lane) : src[(size_t)t * D + d];
+        acc = fmaf(w, v, acc);
+    }
+    if (lane == 0) dst[(size_t)t * D + d] = acc;
+}
+
+template <typename WT> const WT* wptr(float* const* bufs, uint32_t b, uint32_t off) { return reinterpret_cast<const WT*>(bufs[b]) + off; }
+
+}  // namespace
+
+#define ZG_SEQ_CHECK()                                                                                          \
+    do {                                                                                                        \
+        cudaError_t _e = cudaGetLastError();                                                                    \
+        if (_e != cudaSuccess) { zg_set_error("sequence op %u: launch failed: %s", op.tag, cudaGetErrorString(_e)); return false; } \
+        ZG_COUNT_LAUNCH();                                                                                      \
+    } while (0)
+// run `call` with WT = the op's weight type
+#define ZG_SEQ_WDT(wdt, ...)                                                          \
+    do {                                                                              \
+        if ((wdt) == ZG_W_BF16) { typedef bf16 WT; __VA_ARGS__; } else { typedef float WT; __VA_ARGS__; } \
+    } while (0)
+
+uint32_t zg_delta_row_slices(uint32_t dim) {
+    uint32_t rs = 1;
+    while (rs * kDeltaRows < dim) rs <<= 1;
+    return rs;
+}
+
+// Static checks of a sequence op against the program's buffer sizes (f32 slots): shapes, strides and every extent.
+bool zg_seq_op_valid(const ZgOp& op, const size_t* elems, size_t n_bufs, char* why, size_t why_n) {
+    const ZgSeqOp& s = op.u.seq;
+    auto fail = [&](const char* m) { snprintf(why, why_n, "%s", m); return false; };
+    auto have = [&](int i) { return s.buf[i] != ZG_NO_BUF && s.buf[i] < n_bufs; };
+    auto fits = [&](int i, size_t off, size_t n) { return have(i) && off + n <= elems[s.buf[i]]; };
+    const uint32_t wdt_of[] = {s.n[2], s.n[5], s.n[3], 0, s.n[6], s.n[9], s.n[4], s.n[5]};
+    const uint32_t wdt = wdt_of[op.tag - ZG_OP_EMBED];
+    if (wdt > ZG_W_BF16) return fail("unknown weight type");
+    auto wfits = [&](int i, size_t off, size_t n) { return have(i) && (wdt == ZG_W_BF16 ? (off + n + 1) / 2 : off + n) <= elems[s.buf[i]]; };
+    switch (op.tag) {
+        case ZG_OP_EMBED: {
+            const size_t T = s.n[0], D = s.n[1];
+            if (!fits(0, 0, T * D) || !fits(1, ZG_CTL_IDS, T) || !have(2)) return fail("embed: extent");
+            return true;
+        }
+        case ZG_OP_LINEAR: {
+            const size_t M = s.n[0], N = s.n[1], K = s.n[2], srs = s.n[3], drs = s.n[4];
+            if (!M || !N || !K || srs < K || drs < N) return fail("linear: shape");
+            if (!fits(0, s.off[3], (M - 1) * drs + N) || !fits(1, s.off[2], (M - 1) * srs + K) || !wfits(2, s.off[0], N * K)) return fail("linear: extent");
+            if (s.buf[3] != ZG_NO_BUF && !wfits(3, s.off[1], N)) return fail("linear: bias extent");
+            if (s.buf[0] == s.buf[1]) return fail("linear: in place");
+            return true;
+        }
+        case ZG_OP_NORM: {
+            const size_t n = (size_t)s.n[0] * s.n[1];
+            if (!n || s.n[2] > 1) return fail("norm: shape");
+            if (!fits(0, 0, n) || !fits(1, 0, n) || !wfits(2, s.off[0], s.n[1])) return fail("norm: extent");
+            if (s.buf[3] != ZG_NO_BUF && !fits(3, 0, n)) return fail("norm: residual extent");
+            return true;
+        }
+        case ZG_OP_WINDOW_ATTENTION: {
+            const size_t T = s.n[0], H = s.n[1], G = s.n[2], dim = s.n[3], rs = s.n[4], win = s.n[5], R = s.n[6];
+            if (!T || !H || !G || H % G || !dim || dim > kAttnMaxDim || !win || R < win - 1 + T) return fail("window_attention: shape");
+            if (s.off[0] + H * dim > rs || s.off[1] + G * dim > rs || s.off[2] + H * dim > rs) return fail("window_attention: columns");
+            if (!fits(0, 0, T * H * dim) || !fits(1, 0, T * rs) || !have(2) || elems[s.buf[2]] % (R * G * dim) || !fits(3, 0, win * H) || !fits(4, 0, ZG_CTL_IDS))
+                return fail("window_attention: extent");
+            return true;
+        }
+        case ZG_OP_CAUSAL_CONV: {
+            const size_t T = s.n[0], C = s.n[1], taps = s.n[2], srs = s.n[3], drs = s.n[4];
+            if (!T || !C || taps < 1 || srs < C || drs < C || s.n[5] > 1) return fail("causal_conv: shape");
+            if (!fits(0, s.off[2], (T - 1) * drs + C) || !fits(1, s.off[1], (T - 1) * srs + C) || !wfits(2, s.off[0], C * taps) || !have(3) || !fits(4, 0, ZG_CTL_IDS))
+                return fail("causal_conv: extent");
+            if (taps > 1 && elems[s.buf[3]] % ((taps - 1) * C)) return fail("causal_conv: state size");
+            if (s.buf[0] == s.buf[1]) return fail("causal_conv: in place");
+            return true;
+        }
+        case ZG_OP_DELTA_RULE: {
+            const size_t T = s.n[0], H = s.n[1], G = s.n[2], dim = s.n[3], vdim = s.n[4];
+            if (!T || !H || !G || H % G || !dim || !vdim || zg_delta_row_slices((uint32_t)dim) > 32) return fail("delta_rule: shape");
+            if (s.off[0] + G * dim > s.n[5] || s.off[1] + G * dim > s.n[5] || s.off[2] + H * vdim > s.n[5] || s.off[3] + H > s.n[6] || H * dim > s.n[7] || H * vdim > s.n[8])
+                return fail("delta_rule: columns");
+            if (!fits(0, 0, T * H * vdim) || !fits(1, 0, T * s.n[5]) || !fits(2, 0, T * s.n[6]) || !fits(3, 0, T * s.n[7]) || !fits(4, 0, T * s.n[8]) ||
+                !wfits(5, s.off[4], H) || !wfits(5, s.off[5], H * dim) || !wfits(5, s.off[6], vdim) || !have(6) || elems[s.buf[6]] % (H * dim * vdim) || !fits(7, 0, ZG_CTL_IDS))
+                return fail("delta_rule: extent");
+            return true;
+        }
+        case ZG_OP_ROUTE: {
+            const size_t T = s.n[0], NE = s.n[1], top = s.n[2], rs = s.n[3];
+            if (!T || !NE || !top || top > NE || rs < NE || NE > 4096) return fail("route: shape");
+            if (!fits(0, 0, T * top * 2) || !fits(1, s.off[1], (T - 1) * rs + NE) || !wfits(2, s.off[0], NE)) return fail("route: extent");
+            return true;
+        }
+        case ZG_OP_MOE_FFN: {
+            const size_t T = s.n[0], D = s.n[1], ff = s.n[2], E = s.n[3], top = s.n[4];
+            if (!T || !D || !top) return fail("moe_ffn: shape");
+            if (!fits(0, 0, T * D) || !fits(1, 0, T * D) || !fits(2, 0, T * top * 2) || !fits(4, 0, T * top * ff) ||
+                (E && (!wfits(3, s.off[0], E * ff * D) || !wfits(3, s.off[1], E * ff * D) || !wfits(3, s.off[2], E * ff * D))))
+                return fail("moe_ffn: extent");
+            if (s.buf[0] == s.buf[1]) return fail("moe_ffn: in place");
+            return true;
+        }
+        default: return fail("not a sequence op");
+    }
+}
+
+// which of buf[0..8) an op writes (bit i); everything else it names is read
+uint32_t zg_seq_op_writes(uint32_t tag) {
+    switch (tag) {
+        case ZG_OP_WINDOW_ATTENTION: return 1u | (1u << 2);
+        case ZG_OP_CAUSAL_CONV: return 1u | (1u << 3);
+        case ZG_OP_DELTA_RULE: return 1u | (1u << 6);
+        case ZG_OP_MOE_FFN: return 1u | (1u << 4);
+        default: return 1u;
+    }
+}
+
+bool zg_launch_seq_op(ZgCudaCtx* ctx, const ZgOp& op, float* const* bufs, cudaStream_t st) {
+    (void)ctx;
+    const ZgSeqOp& s = op.u.seq;
+    switch (op.tag) {
+        case ZG_OP_EMBED:
+            ZG_SEQ_WDT(s.n[2], k_embed<WT><<<s.n[0], 128, 0, st>>>(bufs[s.buf[0]], bufs[s.buf[1]], wptr<WT>(bufs, s.buf[2], s.off[0]), s.n[1], s.f[0]));
+            ZG_SEQ_CHECK();
+            return true;
+        case ZG_OP_LINEAR: {
+            const uint32_t M = s.n[0], N = s.n[1], K = s.n[2];
+            float* dst = bufs[s.buf[0]] + s.off[3];
+            const float* src = bufs[s.buf[1]] + s.off[2];
+            const bool has_bias = s.buf[3] != ZG_NO_BUF;
+            ZG_SEQ_WDT(s.n[5], {
+                const WT* W = wptr<WT>(bufs, s.buf[2], s.off[0]);
+                const WT* b = has_bias ? wptr<WT>(bufs, s.buf[3], s.off[1]) : nullptr;
+                constexpr uint32_t V = WVec<WT>::n;
+                if (M <= kGemvRows) {
+                    const bool vec = K % V == 0 && (reinterpret_cast<size_t>(W) & 15) == 0 && (reinterpret_cast<size_t>(src) & 15) == 0 && s.n[3] % 4 == 0;
+                    const dim3 grid((N + 7) / 8);
+                    if (vec && M == 1) k_linear_rows_vec<WT, 1><<<grid, 256, 0, st>>>(dst, src, W, b, M, N, K, s.n[3], s.n[4]);
+                    else if (vec && M <= 4) k_linear_rows_vec<WT, 4><<<grid, 256, 0, st>>>(dst, src, W, b, M, N, K, s.n[3], s.n[4]);
+                    else if (vec) k_linear_rows_vec<WT, 8><<<grid, 256, 0, st>>>(dst, src, W, b, M, N, K, s.n[3], s.n[4]);
+                    else k_linear_rows<WT><<<grid, 256, 0, st>>>(dst, src, W, b, M, N, K, s.n[3], s.n[4]);
+                } else {
+                    const dim3 grid((N + kTN - 1) / kTN, (M + kTM - 1) / kTM);
+                    k_linear_tile<WT><<<grid, 256, 0, st>>>(dst, src, W, b, M, N, K, s.n[3], s.n[4]);
+                }
+            });
+            ZG_SEQ_CHECK();
+            return true;
+        }
+        case ZG_OP_NORM: {
+            const float* res = s.buf[3] != ZG_NO_BUF ? bufs[s.buf[3]] : nullptr;
+            ZG_SEQ_WDT(s.n[3], k_norm<WT><<<s.n[0], 256, 0, st>>>(bufs[s.buf[0]], bufs[s.buf[1]], wptr<WT>(bufs, s.buf[2], s.off[0]), res, s.n[1], s.n[2], s.f[0]));
+            ZG_SEQ_CHECK();
+            return true;
+        }
+        case ZG_OP_WINDOW_ATTENTION: {
+            const uint32_t T = s.n[0], H = s.n[1], G = s.n[2], dim = s.n[3];
+            k_ring_append<<<T, 128, 0, st>>>(bufs[s.buf[2]], bufs[s.buf[1]], bufs[s.buf[4]], s.off[1], s.n[4], G * dim, s.n[6]);
+            ZG_SEQ_CHECK();
+            const uint32_t warps = 4;
+            k_window_attention<<<(T * H + warps - 1) / warps, warps * 32, warps * dim * sizeof(float), st>>>(
+                bufs[s.buf[0]], bufs[s.buf[1]], bufs[s.buf[2]], bufs[s.buf[3]], bufs[s.buf[4]], T, H, G, dim, s.n[4], s.off[0], s.off[2], s.n[5], s.n[6], s.f[0], s.f[1]);
+            ZG_SEQ_CHECK();
+            return true;
+        }
+        case ZG_OP_CAUSAL_CONV: {
+            const uint32_t T = s.n[0], C = s.n[1], taps = s.n[2];
+            float* dst = bufs[s.buf[0]] + s.off[2];
+            const float* src = bufs[s.buf[1]] + s.off[1];
+            const size_t n = (size_t)T * C;
+            ZG_SEQ_WDT(s.n[6], k_causal_conv<WT><<<(unsigned)((n + 255) / 256), 256, 0, st>>>(dst, src, wptr<WT>(bufs, s.buf[2], s.off[0]), bufs[s.buf[3]], bufs[s.buf[4]],
+                                                                                          T, C, taps, s.n[3], s.n[4], s.n[5]));
+            ZG_SEQ_CHECK();
+            if (taps > 1) {
+                k_conv_advance<<<(C + 127) / 128, 128, 0, st>>>(bufs[s.buf[3]], src, bufs[s.buf[4]], T, C, taps, s.n[3]);
+                ZG_SEQ_CHECK();
+            }
+            return true;
+        }
+        case ZG_OP_DELTA_RULE: {
+            const uint32_t T = s.n[0], H = s.n[1], G = s.n[2], dim = s.n[3], vdim = s.n[4];
+            const uint32_t RS = zg_delta_row_slices(dim), cols = kDeltaThreads / RS;
+            const size_t smem = ((size_t)3 * kDeltaTile * RS * kDeltaRows + kDeltaTile) * sizeof(float);
+            const dim3 grid((vdim + cols - 1) / cols, H);
+            ZG_SEQ_WDT(s.n[9], {
+                if (smem > 48 * 1024) cudaFuncSetAttribute(k_delta_rule<WT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                k_delta_rule<WT><<<grid, kDeltaThreads, smem, st>>>(bufs[s.buf[0]], bufs[s.buf[1]], bufs[s.buf[2]], bufs[s.buf[3]], wptr<WT>(bufs, s.buf[5], 0), bufs[s.buf[6]],
+                                                                  bufs[s.buf[7]], T, H, G, dim, vdim, RS, s.off[0], s.off[1], s.off[2], s.off[3], s.off[4], s.off[5],
+                                                                  s.n[5], s.n[6], s.n[7], s.f[1], s.f[2]);
+            });
+            ZG_SEQ_CHECK();
+            ZG_SEQ_WDT(s.n[9], k_delta_out<WT><<<(T * H + 3) / 4, 128, 0, st>>>(bufs[s.buf[0]], bufs[s.buf[4]], wptr<WT>(bufs, s.buf[5], 0), T * H, H, vdim, s.n[8], s.off[6], s.f[0]));
+            ZG_SEQ_CHECK();
+            return true;
+        }
+        case ZG_OP_ROUTE: {
+            const uint32_t T = s.n[0], NE = s.n[1];
+            ZG_SEQ_WDT(s.n[4], k_route<WT><<<(T + 3) / 4, 128, 4 * NE * sizeof(float), st>>>(bufs[s.buf[0]], bufs[s.buf[1]] + s.off[1], wptr<WT>(bufs, s.buf[2], s.off[0]), T, NE,
+                                                                                         s.n[2], s.n[3]));
+            ZG_SEQ_CHECK();
+            return true;
+        }
+        case ZG_OP_MOE_FFN: {
+            const uint32_t T = s.n[0], D = s.n[1], ff = s.n[2], E = s.n[3], top = s.n[4];
+            ZG_SEQ_WDT(s.n[5], {
+                if (E && ff) {
+                    k_moe_up<WT><<<dim3((ff + 7) / 8, T * top), 256, 0, st>>>(bufs[s.buf[4]], bufs[s.buf[1]], bufs[s.buf[2]], wptr<WT>(bufs, s.buf[3], s.off[0]),
+                                                                           wptr<WT>(bufs, s.buf[3], s.off[1]), D, ff, E, top, s.f[0], s.f[1]);
+                    ZG_COUNT_LAUNCH();
+                }
+                k_moe_down<WT><<<dim3((D + 7) / 8, T), 256, 0, st>>>(bufs[s.buf[0]], bufs[s.buf[1]], bufs[s.buf[4]], bufs[s.buf[2]], wptr<WT>(bufs, s.buf[3], s.off[2]), D, ff, E, top);
+            });
+            ZG_SEQ_CHECK();
+            return true;
+        }
+        default:
+            zg_set_error("unsupported sequence op tag %u", op.tag);
+            return false;
+    }
+}

@@ -366,3 +366,9 @@ bool zg_kvq_launch_attention(const ZgKvqAttn* d_tab, uint32_t count, uint32_t se
 // comm.cu : NCCL through dlopen (no link-time dependency)
 bool zg_comm_allreduce(ZgCudaCtx* ctx, float* buf, size_t n, cudaStream_t st);
 bool zg_comm_allgather(ZgCudaCtx* ctx, const float* src, float* dst, size_t n_per_rank, cudaStream_t st);
+
+// seqops.cu : the sequence-model ops (ZG_OP_EMBED .. ZG_OP_MOE_FFN)
+inline bool zg_is_seq_op(uint32_t tag) { return tag >= ZG_OP_EMBED && tag < ZG_OP_END; }
+bool zg_seq_op_valid(const ZgOp& op, const size_t* elems, size_t n_bufs, char* why, size_t why_n);
+uint32_t zg_seq_op_writes(uint32_t tag);
+bool zg_launch_seq_op(ZgCudaCtx* ctx, const ZgOp& op, float* const* bufs, cudaStream_t st);

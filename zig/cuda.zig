@@ -44,6 +44,7 @@ const ZgOp = extern struct {
         // extensions (tags 12 / 13): collectives of a row-sharded program; zgml's DeviceOp has no such variants yet
         allreduce: extern struct { buf: u32, offset: u32, n: u32 },
         allgather: extern struct { dst: u32, src: u32, n: u32, dst_offset: u32, src_offset: u32 },
+        seq: extern struct { buf: [8]u32, off: [8]u32, n: [10]u32, f: [4]f32 }, // sequence-model extensions (not emitted by zgml)
     },
 };
 const ZgIO = extern struct { buf_idx: u32, offset: u32, host_ptr: ?*anyopaque, size: u32, _pad: u32 = 0 };
@@ -51,6 +52,7 @@ const ZgQWeight = extern struct { data: [*]const i8, n_data: usize, scales: [*]c
 const ZgProgram = extern struct {
     ops: [*]const ZgOp, n_ops: usize, n_buffers: usize, buffer_sizes: [*]const usize,
     initial_uploads: [*]const ZgIO, n_uploads: usize, qweights: [*]const ZgQWeight, n_qweights: usize,
+    externs: ?*const anyopaque = null, n_externs: usize = 0, // caller-owned buffers (extension; unused by zgml's programs)
 };
 const ZgProfile = extern struct { time_ns: [12]u64, backend_op_count: u64, fallback_op_count: u64, backend_dispatch_count: u64, sync_time_ns: u64, sync_count: u64, call_count: u32, _pad: u32 };
 
