@@ -1,0 +1,210 @@
+"""Lududra on the CUDA backend against the float64 restatement (tests/lududra_reference.py): every mechanism alone,
+whole prompts, token-by-token decoding through the carried state, prompts cut into portions, interleaved requests in
+several state slots, slot reuse, long decoding across many turns of the key ring, shapes of many kinds, and greedy
+generation through the registry's entry point."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+import lududra_reference as ref
+from lududra_models import as_f64, attention_layer, config, delta_layer, moe, random_weights
+
+pytestmark = pytest.mark.gpu
+
+TOL = 2e-4   # of the logits' scale; f32 accumulation against float64
+
+
+def open_model(be, cfg, W, dtype="bfloat16", n_slots=1, max_chunk=16, keep_layers=False):
+    from zgml_b200.host.lududra import LududraConfig, LududraModel
+    from zgml_b200.host.session import SequenceSession
+    model = LududraModel(be, LududraConfig.from_dict(cfg), lambda n: W[n], dtype)
+    return SequenceSession(be, model, n_slots=n_slots, max_chunk=max_chunk, keep_layers=keep_layers)
+
+
+def close(s):
+    s.close()
+    s.model.close()
+
+
+def rel(got, want):
+    return float(np.max(np.abs(got.astype(np.float64) - want)) / (np.max(np.abs(want)) + 1e-30))
+
+
+def tokens(cfg, n, seed=1):
+    return np.random.default_rng(seed).integers(0, cfg["vocab"], n).tolist()
+
+
+MIXED = config([delta_layer(mlp=moe()), attention_layer(mlp=moe(experts=5, identity=2, top=3)), delta_layer(heads=2, kv_heads=2, dim=8, vdim=8, conv=2),
+                attention_layer(heads=2, kv_heads=1, dim=24, window=5, rel_rows=6, bias_max=9, softcap=4.0)])
+
+
+# ── each mechanism alone (a one-layer model without a feed-forward isolates its mixer) ──
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+@pytest.mark.parametrize("layer", [
+    attention_layer(),
+    attention_layer(heads=3, kv_heads=3, dim=40, window=3, rel_rows=4, bias_max=3),      # window shorter than the table's linear half
+    attention_layer(heads=6, kv_heads=1, dim=8, window=33, rel_rows=10, bias_max=20, softcap=2.0),   # window crosses the 32-key block
+    delta_layer(),
+    delta_layer(heads=3, kv_heads=1, dim=40, vdim=10, conv=4, rank_a=3, rank_g=5),        # padded key rows, several row slices
+    delta_layer(heads=2, kv_heads=2, dim=8, vdim=70, conv=1),                            # no carried inputs; columns over two CTAs
+    delta_layer(heads=1, kv_heads=1, dim=130, vdim=12, conv=2),                          # sixteen row slices
+], ids=["attn", "attn-short-window", "attn-33", "delta", "delta-odd", "delta-notail", "delta-wide-key"])
+def test_mixer_alone(cuda_backend, layer, dtype):
+    cfg = config([layer], width=40, vocab=61)
+    W = random_weights(cfg, seed=5, qk_gain=4.0)
+    toks = tokens(cfg, 45)
+    want, stream = ref.forward(cfg, as_f64(W), toks)
+    s = open_model(cuda_backend, cfg, W, dtype, max_chunk=64, keep_layers=True)
+    got = s.feed("a", toks[:32] + toks[32:40] + toks[40:44] + toks[44:], range(45))
+    assert rel(got, want) < TOL
+    close(s)
+
+
+@pytest.mark.parametrize("mlp", [moe(), moe(experts=3, identity=0, top=1, ff=7, limit=0.5), moe(experts=2, identity=3, top=4, ff=40),
+                                 moe(experts=9, identity=1, top=2, ff=16, limit=100.0)],
+                         ids=["moe", "top1-no-identity", "mostly-identity", "unclamped"])
+def test_feed_forward(cuda_backend, mlp):
+    """The residual after the layer is compared too, so a fault in routing, clamping or the identity experts cannot hide
+    behind the final norm."""
+    cfg = config([attention_layer(heads=2, kv_heads=2, dim=8, window=4, mlp=mlp)], width=36, vocab=50)
+    W = random_weights(cfg, seed=9)
+    toks = tokens(cfg, 19)
+    want, stream = ref.forward(cfg, as_f64(W), toks)
+    s = open_model(cuda_backend, cfg, W, "float32", max_chunk=32, keep_layers=True)
+    got = s.feed("a", toks[:16], range(16))
+    layers = s.layer_streams(16, "all")
+    assert rel(layers[0], stream[0][:16]) < TOL
+    assert rel(got, want[:16]) < TOL
+    close(s)
+
+
+def test_layer_streams_of_a_mixed_stack(cuda_backend):
+    W = random_weights(MIXED, seed=2)
+    toks = tokens(MIXED, 16)
+    want, stream = ref.forward(MIXED, as_f64(W), toks)
+    s = open_model(cuda_backend, MIXED, W, "float32", keep_layers=True)
+    got = s.feed("a", toks, range(16))
+    layers = s.layer_streams(16, "all")
+    for i in range(len(MIXED["layers"])):
+        assert rel(layers[i], stream[i]) < TOL, f"layer {i}"
+    assert rel(got, want) < TOL
+    close(s)
+
+
+# ── prefill against decoding, portions, first tokens ──
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_prefill_equals_token_by_token(cuda_backend, dtype):
+    W = random_weights(MIXED, seed=3, qk_gain=3.0)
+    toks = tokens(MIXED, 40)
+    want, _ = ref.forward(MIXED, as_f64(W), toks)
+    s = open_model(cuda_backend, MIXED, W, dtype, n_slots=2)
+    whole = s.feed("whole", toks, range(40))
+    single = np.concatenate([s.feed("single", [t], [0]) for t in toks])
+    assert rel(whole, want) < TOL and rel(single, want) < TOL
+    assert rel(whole[:3], want[:3]) < TOL   # the first tokens see zeros before the start, not a stale tail or ring
+    close(s)
+
+
+@pytest.mark.parametrize("cuts", [[2, 2, 2, 30, 3, 2, 9], [1, 16, 1, 15, 17], [7, 7, 7, 7, 7, 7, 8], [50]])
+def test_portions(cuda_backend, cuts):
+    W = random_weights(MIXED, seed=4, qk_gain=3.0)
+    toks = tokens(MIXED, 50)
+    want, _ = ref.forward(MIXED, as_f64(W), toks)
+    s = open_model(cuda_backend, MIXED, W, max_chunk=16)
+    got, at = [], 0
+    for c in cuts:
+        got.append(s.feed("r", toks[at:at + c], range(c)))
+        at += c
+    assert rel(np.concatenate(got), want) < TOL
+    close(s)
+
+
+# ── window edges, in prompts and in decoding, with a peaky softmax ──
+@pytest.mark.parametrize("window", [1, 2, 7, 16, 17])
+def test_window_edges(cuda_backend, window):
+    cfg = config([attention_layer(heads=2, kv_heads=1, dim=16, window=window, rel_rows=6, bias_max=12, softcap=60.0)], width=32, vocab=40)
+    W = random_weights(cfg, seed=window, qk_gain=12.0)
+    toks = tokens(cfg, 3 * window + 9)
+    n = len(toks)
+    want, _ = ref.forward(cfg, as_f64(W), toks)
+    # the weights are peaky enough that one key more or less is far outside the tolerance
+    wider = json.loads(json.dumps(cfg))
+    wider["layers"][0]["mixer"]["mask"]["size"] = window + 1
+    assert rel(ref.forward(wider, as_f64(W), toks)[0], want) > 50 * TOL
+    s = open_model(cuda_backend, cfg, W, n_slots=2, max_chunk=8)
+    assert rel(s.feed("prompt", toks, range(n)), want) < TOL
+    half = n // 2
+    got = [s.feed("decode", toks[:half], range(half))] + [s.feed("decode", [t], [0]) for t in toks[half:]]
+    assert rel(np.concatenate(got), want) < TOL
+    close(s)
+
+
+def test_sink_matters_and_is_there(cuda_backend):
+    """Negative scores everywhere: the sink takes most of the weight, so leaving it out would change the output a lot."""
+    cfg = config([attention_layer(heads=2, kv_heads=2, dim=8, window=6, softcap=1e4)], width=24, vocab=30)
+    W = random_weights(cfg, seed=11, qk_gain=0.0)          # q = q.b, k = k.b: all scores equal q.b . k.b
+    W["l0.mix.q.b"] = np.abs(W["l0.mix.q.b"]) * 4
+    W["l0.mix.k.b"] = -np.abs(W["l0.mix.k.b"]) * 4
+    W["l0.mix.rel"] = np.zeros_like(W["l0.mix.rel"])
+    toks = tokens(cfg, 12)
+    want, _ = ref.forward(cfg, as_f64(W), toks)
+    s = open_model(cuda_backend, cfg, W, "float32")
+    assert rel(s.feed("a", toks, range(12)), want) < TOL
+    close(s)
+
+
+# ── batches of unequal requests, slots freed and used again ──
+def test_interleaved_requests_and_slot_reuse(cuda_backend):
+    W = random_weights(MIXED, seed=6)
+    A, B, C = tokens(MIXED, 30, 1), tokens(MIXED, 11, 2), tokens(MIXED, 23, 3)
+    wa, wb, wc = (ref.forward(MIXED, as_f64(W), t)[0] for t in (A, B, C))
+    s = open_model(cuda_backend, MIXED, W, n_slots=2, max_chunk=8)
+    ga, gb = [], []
+    r = s.step([{"id": "a", "tokens": A[:9], "want": range(9)}, {"id": "b", "tokens": B[:2], "want": range(2)}])
+    ga.append(r[0]), gb.append(r[1])
+    r = s.step([{"id": "b", "tokens": B[2:], "want": range(9)}, {"id": "a", "tokens": A[9:10], "want": [0]}], end=["b"])
+    gb.append(r[0]), ga.append(r[1])
+    with pytest.raises(KeyError):
+        s.pool.slot("b")
+    # c takes b's slot: nothing of b's recurrent state, convolution tail or keys may show
+    r = s.step([{"id": "c", "tokens": C, "want": range(23)}, {"id": "a", "tokens": A[10:], "want": range(20)}], end=["a", "c"])
+    ga.append(r[1])
+    assert rel(np.concatenate(ga), wa) < TOL and rel(np.concatenate(gb), wb) < TOL and rel(r[0], wc) < TOL
+    with pytest.raises(RuntimeError):
+        s.step([{"id": i, "tokens": [1], "want": []} for i in "xyz"])   # more live requests than slots
+    close(s)
+
+
+def test_long_decoding_turns_the_ring_many_times(cuda_backend):
+    cfg = config([attention_layer(heads=2, kv_heads=1, dim=16, window=9, mlp=moe()), delta_layer(mlp=None)], width=32, vocab=64)
+    W = random_weights(cfg, seed=8, qk_gain=3.0)
+    toks = tokens(cfg, 150)
+    want, _ = ref.forward(cfg, as_f64(W), toks)
+    s = open_model(cuda_backend, cfg, W, max_chunk=4)      # ring of 12 rows
+    got = [s.feed("r", toks[:6], range(6))] + [s.feed("r", [t], [0]) for t in toks[6:]]
+    assert rel(np.concatenate(got), want) < 2 * TOL
+    close(s)
+
+
+# ── the entry point a user calls ──
+def test_registry_loads_a_folder_and_generates_greedily(cuda_backend, tmp_path):
+    from zgml_b200.host.registry import open_session
+    from zgml_b200.host.safetensors import write_safetensors
+    W = random_weights(MIXED, seed=12)
+    public = json.loads(json.dumps(MIXED))
+    for L in public["layers"]:
+        L["mixer"] = {k: v for k, v in L["mixer"].items() if not k.startswith("_")}
+    with open(os.path.join(tmp_path, "config.json"), "w") as f:
+        json.dump(public, f)
+    write_safetensors(os.path.join(tmp_path, "model.safetensors"), W)
+    prompt = tokens(MIXED, 13)
+    seq = list(prompt)
+    for _ in range(10):
+        seq.append(int(np.argmax(ref.forward(MIXED, as_f64(W), seq)[0][-1])))
+    for dtype in ("bfloat16", "float32"):
+        s = open_session(cuda_backend, str(tmp_path), dtype, max_chunk=8)
+        assert s.generate(prompt, 10) == seq[13:]
+        assert s.pool.live() == []
+        close(s)

@@ -24,13 +24,28 @@ def _newer(target, sources):
 
 
 def build_cuda(force=False, verbose=False):
+    """One object per translation unit, compiled in parallel and only when its source or a shared header changed, then
+    linked into the library (a full build is bound by the slowest file instead of their sum)."""
+    from concurrent.futures import ThreadPoolExecutor
     srcs = sorted(glob.glob(os.path.join(CSRC, "*.cu")))
-    deps = srcs + glob.glob(os.path.join(CSRC, "*.cuh")) + [os.path.join(ROOT, "include", "zgml_cuda.h")]
-    if not force and _newer(LIB, deps):
+    hdrs = glob.glob(os.path.join(CSRC, "*.cuh")) + [os.path.join(ROOT, "include", "zgml_cuda.h")]
+    if not force and _newer(LIB, srcs + hdrs):
         return LIB
-    os.makedirs(LIB_DIR, exist_ok=True)
-    cmd = ["nvcc"] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-o", LIB] + srcs
-    subprocess.run(cmd, check=True)
+    obj_dir = os.path.join(LIB_DIR, "obj")
+    os.makedirs(obj_dir, exist_ok=True)
+    compile_flags = [f for f in NVCC_FLAGS if f != "-shared"]
+
+    def compile_one(src):
+        obj = os.path.join(obj_dir, os.path.basename(src)[:-3] + ".o")
+        if force or not _newer(obj, [src] + hdrs):
+            subprocess.run(["nvcc"] + compile_flags + (["-Xptxas", "-v"] if verbose else []) + ["-c", "-o", obj, src], check=True)
+        return obj
+
+    with ThreadPoolExecutor(max_workers=min(len(srcs), os.cpu_count() or 4)) as pool:
+        objs = list(pool.map(compile_one, srcs))
+    tmp = LIB + f".{os.getpid()}.tmp"
+    subprocess.run(["nvcc"] + NVCC_FLAGS + ["-o", tmp] + objs, check=True)
+    os.replace(tmp, LIB)
     return LIB
 
 

@@ -527,7 +527,7 @@ bool zg_seq_op_valid(const ZgOp& op, const size_t* elems, size_t n_bufs, char* w
             const size_t T = s.n[0], H = s.n[1], G = s.n[2], dim = s.n[3], rs = s.n[4], win = s.n[5], R = s.n[6];
             if (!T || !H || !G || H % G || !dim || dim > kAttnMaxDim || !win || R < win - 1 + T) return fail("window_attention: shape");
             if (s.off[0] + H * dim > rs || s.off[1] + G * dim > rs || s.off[2] + H * dim > rs) return fail("window_attention: columns");
-            if (!fits(0, 0, T * H * dim) || !fits(1, 0, T * rs) || !have(2) || elems[s.buf[2]] % (R * G * dim) || !fits(3, 0, win * H) || !fits(4, 0, ZG_CTL_IDS))
+            if (!fits(0, 0, T * H * dim) || !fits(1, 0, T * rs) || !have(2) || elems[s.buf[2]] < R * G * dim || !fits(3, 0, win * H) || !fits(4, 0, ZG_CTL_IDS))
                 return fail("window_attention: extent");
             return true;
         }
@@ -536,7 +536,7 @@ bool zg_seq_op_valid(const ZgOp& op, const size_t* elems, size_t n_bufs, char* w
             if (!T || !C || taps < 1 || srs < C || drs < C || s.n[5] > 1) return fail("causal_conv: shape");
             if (!fits(0, s.off[2], (T - 1) * drs + C) || !fits(1, s.off[1], (T - 1) * srs + C) || !wfits(2, s.off[0], C * taps) || !have(3) || !fits(4, 0, ZG_CTL_IDS))
                 return fail("causal_conv: extent");
-            if (taps > 1 && elems[s.buf[3]] % ((taps - 1) * C)) return fail("causal_conv: state size");
+            if (taps > 1 && elems[s.buf[3]] < (taps - 1) * C) return fail("causal_conv: state size");
             if (s.buf[0] == s.buf[1]) return fail("causal_conv: in place");
             return true;
         }
@@ -546,7 +546,7 @@ bool zg_seq_op_valid(const ZgOp& op, const size_t* elems, size_t n_bufs, char* w
             if (s.off[0] + G * dim > s.n[5] || s.off[1] + G * dim > s.n[5] || s.off[2] + H * vdim > s.n[5] || s.off[3] + H > s.n[6] || H * dim > s.n[7] || H * vdim > s.n[8])
                 return fail("delta_rule: columns");
             if (!fits(0, 0, T * H * vdim) || !fits(1, 0, T * s.n[5]) || !fits(2, 0, T * s.n[6]) || !fits(3, 0, T * s.n[7]) || !fits(4, 0, T * s.n[8]) ||
-                !wfits(5, s.off[4], H) || !wfits(5, s.off[5], H * dim) || !wfits(5, s.off[6], vdim) || !have(6) || elems[s.buf[6]] % (H * dim * vdim) || !fits(7, 0, ZG_CTL_IDS))
+                !wfits(5, s.off[4], H) || !wfits(5, s.off[5], H * dim) || !wfits(5, s.off[6], vdim) || !have(6) || elems[s.buf[6]] < H * dim * vdim || !fits(7, 0, ZG_CTL_IDS))
                 return fail("delta_rule: extent");
             return true;
         }
