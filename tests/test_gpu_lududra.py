@@ -208,3 +208,53 @@ def test_registry_loads_a_folder_and_generates_greedily(cuda_backend, tmp_path):
         assert s.generate(prompt, 10) == seq[13:]
         assert s.pool.live() == []
         close(s)
+
+
+# ── the tensor-core prefill matmul (bfloat16 sessions, more than 8 rows) ──
+@pytest.mark.parametrize("M,N,K,bias", [(128, 128, 64, False), (200, 300, 136, True), (9, 64, 72, True), (300, 72, 520, False)])
+def test_dense_tensor_core_linear_alone(cuda_backend, M, N, K, bias):
+    """One LINEAR op over bfloat16 weights: equal to the float64 product of the bf16-rounded activations (the only rounding
+    the tensor path adds), including ragged tile edges in M, N and K and a strided source."""
+    from lududra_models import bf16_exact
+    from zgml_b200 import DeviceBuffer, DeviceOp, DeviceProgram, ExternBuffer, ProgramIO, abi
+    from zgml_b200.host.safetensors import f32_to_bf16_bits
+    r = np.random.default_rng(M + N + K)
+    W, b = bf16_exact(r.standard_normal((N, K)).astype(np.float32)), bf16_exact(r.standard_normal(N).astype(np.float32))
+    x = r.standard_normal((M, K + 8)).astype(np.float32)
+    arena = np.concatenate([W.ravel(), b])
+    buf = DeviceBuffer(cuda_backend, 2 * arena.size, zero=False)
+    buf.upload(f32_to_bf16_bits(arena))
+    op = DeviceOp.linear(1, 0, 2, 0, M, N, K, abi.W_BF16, bias=2 if bias else None, bias_off=N * K, src_off=8, src_rs=K + 8)
+    prog = DeviceProgram([op], [M * (K + 8) + 8, M * N, buf.elems], [], [], [ExternBuffer(2, buf)])
+    h = cuda_backend.compile_program(prog)
+    assert h is not None
+    got = np.zeros((M, N), np.float32)
+    flat = np.concatenate([np.zeros(8, np.float32), x.ravel()])
+    cuda_backend.execute_program(h, [ProgramIO(0, flat)], [ProgramIO(1, got)])
+    stats = cuda_backend.program_stats(h)
+    assert stats["tensor_core_linears"] == 1 and stats["dense_gemm_timeouts"] == 0
+    want = bf16_exact(x[:, :K]).astype(np.float64) @ W.astype(np.float64).T + (b.astype(np.float64) if bias else 0.0)
+    assert rel(got, want) < 2e-6
+    cuda_backend.free_program(h)
+    buf.free()
+
+
+def test_tensor_core_prefill_of_a_wide_model(cuda_backend):
+    """Widths that reach the tensor path: the bfloat16 session's prompt logits stay within the rounding of activations to
+    bf16 of the exact float32 session's, and its decoded continuation (row kernels, f32 activations) agrees with both."""
+    cfg = config([delta_layer(heads=4, kv_heads=2, dim=32, vdim=64, rank_a=16, rank_g=16, mlp=moe(experts=4, identity=1, top=2, ff=64)),
+                  attention_layer(heads=4, kv_heads=2, dim=32, window=40, rel_rows=16, bias_max=64, mlp=moe(experts=4, identity=1, top=2, ff=64))],
+                 width=128, vocab=256)
+    W = random_weights(cfg, seed=21)
+    toks = tokens(cfg, 72)
+    want, _ = ref.forward(cfg, as_f64(W), toks)
+    s16, s32 = open_model(cuda_backend, cfg, W, "bfloat16", max_chunk=64), open_model(cuda_backend, cfg, W, "float32", max_chunk=64)
+    g16 = np.concatenate([s16.feed("r", toks[:64], range(64))] + [s16.feed("r", [t], [0]) for t in toks[64:]])
+    g32 = np.concatenate([s32.feed("r", toks[:64], range(64))] + [s32.feed("r", [t], [0]) for t in toks[64:]])
+    lp, handle, _, _ = s16.program(64, "all")
+    stats = cuda_backend.program_stats(handle)
+    assert stats["tensor_core_linears"] >= 5 and stats["dense_gemm_timeouts"] == 0
+    assert cuda_backend.program_stats(s32.program(64, "all")[1])["tensor_core_linears"] == 0
+    assert rel(g32, want) < TOL
+    assert rel(g16, want) < 3e-2
+    close(s16), close(s32)

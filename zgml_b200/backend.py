@@ -584,7 +584,8 @@ class CudaBackend:
         """Schedule facts of a compiled program: kernels per execution, DeviceOps / layers inside the fused decode kernel."""
         f = self.lib.zg_cuda_program_stats
         return {"kernels": int(f(handle.ptr, 0)), "fused_decode_ops": int(f(handle.ptr, 1)), "fused_decode_layers": int(f(handle.ptr, 2)),
-                "streamed_matvec_launches": int(f(handle.ptr, 3)), "dense_bytes_saved_per_execution": int(f(handle.ptr, 4))}
+                "streamed_matvec_launches": int(f(handle.ptr, 3)), "dense_bytes_saved_per_execution": int(f(handle.ptr, 4)),
+                "dense_gemm_timeouts": int(f(handle.ptr, 5)), "tensor_core_linears": int(f(handle.ptr, 6))}
 
 
 class QuantizedWeight:

@@ -334,6 +334,7 @@ static bool reserve_workspace(ZgCudaProgram* p) {
     p->ws_cnt_off.assign(p->ops.size(), 0);
     for (size_t i = 0; i < p->ops.size(); i++) {
         const ZgOp& op = p->ops[i];
+        if (zg_is_seq_op(op.tag)) { const size_t g = zg_seq_op_scratch_elems(op, p->buffers.data()); if (g > gs) gs = g; continue; }
         if (op.tag != ZG_OP_QMATMUL) continue;
         size_t a = 0, b = 0;
         zg_qgemv_ws_need(p->ctx, p->qweights[op.u.qmatmul.weight_idx], op.u.qmatmul.M, &a, &b);
@@ -422,6 +423,7 @@ static void op_ranges(const ZgCudaProgram* p, const ZgOp& op, std::vector<ZgRang
                 const uint32_t wr = zg_seq_op_writes(op.tag);
                 for (int i = 0; i < 8; i++)
                     if (op.u.seq.buf[i] != ZG_NO_BUF) whole(op.u.seq.buf[i], (wr >> i) & 1u);
+                if (zg_seq_op_scratch_elems(op, p->buffers.data())) span((uint32_t)p->buffers.size(), 0, 1, true);   // one shared activation scratch
             }
             break;
     }
@@ -1718,7 +1720,7 @@ static bool launch_one(ZgCudaProgram* p, size_t i, cudaStream_t st) {
         }
     }
     if (zg_op_is_batched(op.tag)) return zg_launch_batch(op, p->d_batch + p->single_entry[i], 1, p->d_dyn, st);
-    if (zg_is_seq_op(op.tag)) return zg_launch_seq_op(ctx, op, p->buffers.data(), st);
+    if (zg_is_seq_op(op.tag)) return zg_launch_seq_op(ctx, op, p->buffers.data(), p->ws.gemm_scratch, st);
     return zg_launch_op(ctx, op, p->buffers.data(), p->d_dyn, (uint32_t)i, p->d_steps + p->step_off[i], st);
 }
 
@@ -2111,6 +2113,8 @@ extern "C" int zg_cuda_program_promote_dense(ZgCudaCtx* ctx, ZgCudaProgram* p, i
 extern "C" uint64_t zg_cuda_program_stats(const ZgCudaProgram* p, int what) {
     if (!p) return 0;
     switch (what) {
+        case 5: return zg_dense_gemm_timeouts();
+        case 6: { uint64_t n = 0; for (const ZgOp& op : p->ops) if (zg_is_seq_op(op.tag) && zg_seq_op_scratch_elems(op, p->buffers.data())) n++; return n; }
         case 0: return p->graph_kernels;
         case 1: return p->dec.valid ? p->dec_count : 0;
         case 2: return p->dec.valid ? p->dec.plan.n_layers : 0;

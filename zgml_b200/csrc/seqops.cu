@@ -9,6 +9,7 @@
 #include "zg_internal.cuh"
 
 #include <cuda_bf16.h>
+#include <stdlib.h>
 
 namespace {
 
@@ -580,7 +581,17 @@ uint32_t zg_seq_op_writes(uint32_t tag) {
     }
 }
 
-bool zg_launch_seq_op(ZgCudaCtx* ctx, const ZgOp& op, float* const* bufs, cudaStream_t st) {
+// f32 slots of the shared activation scratch this op needs (0: none): a LINEAR over bfloat16 weights with more rows than the
+// row kernels take runs on the tensor cores (dense_gemm.cu) from a bf16 copy of its input.  ZG_DENSE_GEMM=0 keeps the exact tile.
+size_t zg_seq_op_scratch_elems(const ZgOp& op, float* const* bufs) {
+    static const bool enabled = [] { const char* e = getenv("ZG_DENSE_GEMM"); return !(e && e[0] == '0'); }();
+    if (!enabled || op.tag != ZG_OP_LINEAR || op.u.seq.n[5] != ZG_W_BF16) return 0;
+    const ZgSeqOp& s = op.u.seq;
+    if (!zg_dense_gemm_usable(wptr<bf16>(bufs, s.buf[2], s.off[0]), s.n[0], s.n[1], s.n[2])) return 0;
+    return zg_dense_gemm_scratch_elems(s.n[0], s.n[2]);
+}
+
+bool zg_launch_seq_op(ZgCudaCtx* ctx, const ZgOp& op, float* const* bufs, float* scratch, cudaStream_t st) {
     (void)ctx;
     const ZgSeqOp& s = op.u.seq;
     switch (op.tag) {
@@ -593,6 +604,9 @@ bool zg_launch_seq_op(ZgCudaCtx* ctx, const ZgOp& op, float* const* bufs, cudaSt
             float* dst = bufs[s.buf[0]] + s.off[3];
             const float* src = bufs[s.buf[1]] + s.off[2];
             const bool has_bias = s.buf[3] != ZG_NO_BUF;
+            if (scratch && zg_seq_op_scratch_elems(op, bufs))
+                return zg_dense_gemm_launch(wptr<bf16>(bufs, s.buf[2], s.off[0]), has_bias ? wptr<bf16>(bufs, s.buf[3], s.off[1]) : nullptr, src, dst, M, N, K,
+                                            s.n[3], s.n[4], scratch, st);
             ZG_SEQ_WDT(s.n[5], {
                 const WT* W = wptr<WT>(bufs, s.buf[2], s.off[0]);
                 const WT* b = has_bias ? wptr<WT>(bufs, s.buf[3], s.off[1]) : nullptr;

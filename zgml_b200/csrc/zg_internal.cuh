@@ -371,4 +371,11 @@ bool zg_comm_allgather(ZgCudaCtx* ctx, const float* src, float* dst, size_t n_pe
 inline bool zg_is_seq_op(uint32_t tag) { return tag >= ZG_OP_EMBED && tag < ZG_OP_END; }
 bool zg_seq_op_valid(const ZgOp& op, const size_t* elems, size_t n_bufs, char* why, size_t why_n);
 uint32_t zg_seq_op_writes(uint32_t tag);
-bool zg_launch_seq_op(ZgCudaCtx* ctx, const ZgOp& op, float* const* bufs, cudaStream_t st);
+size_t zg_seq_op_scratch_elems(const ZgOp& op, float* const* bufs);   // shared activation scratch the op stages through (0: none)
+bool zg_launch_seq_op(ZgCudaCtx* ctx, const ZgOp& op, float* const* bufs, float* scratch, cudaStream_t st);
+// dense_gemm.cu : bf16 x bf16 -> f32 prefill matmul on tcgen05 (TMA-fed, TMEM accumulator)
+bool zg_dense_gemm_usable(const void* w_bf16, uint32_t M, uint32_t N, uint32_t K);
+size_t zg_dense_gemm_scratch_elems(uint32_t M, uint32_t K);
+unsigned int zg_dense_gemm_timeouts();
+bool zg_dense_gemm_launch(const void* w_bf16, const void* bias_bf16, const float* src, float* dst, uint32_t M, uint32_t N, uint32_t K,
+                          uint32_t src_rs, uint32_t dst_rs, float* scratch, cudaStream_t st);
