@@ -454,6 +454,10 @@ int zg_cuda_comm_mode(const ZgCudaCtx* ctx);
 int zg_cuda_trace(ZgCudaCtx* ctx, int enable);
 size_t zg_cuda_trace_read(ZgCudaCtx* ctx, unsigned long long* host, size_t max_records);
 
+/* f32 slots the scratch operand of a sequence-model op must have (MOE_FFN buf[4]: per-pair activations, or the sorted
+ * rows, per-expert tiles and partial products of the grouped tensor-core form); 0 for ops without one. */
+size_t zg_cuda_seq_scratch_elems(const ZgOp* op);
+
 void* zg_cuda_malloc(ZgCudaCtx* ctx, size_t bytes);
 void zg_cuda_free_device(ZgCudaCtx* ctx, void* p);
 int zg_cuda_memcpy_h2d(ZgCudaCtx* ctx, void* d, const void* h, size_t bytes);

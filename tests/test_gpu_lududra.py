@@ -16,7 +16,12 @@ pytestmark = pytest.mark.gpu
 TOL = 2e-4   # of the logits' scale; f32 accumulation against float64
 
 
-def open_model(be, cfg, W, dtype="bfloat16", n_slots=1, max_chunk=16, keep_layers=False):
+def tol(dtype):
+    """A bfloat16 session rounds the activations that enter a tensor-core matmul (steps of more than 8 tokens) to bf16."""
+    return TOL if dtype == "float32" else 3e-2
+
+
+def open_model(be, cfg, W, dtype="float32", n_slots=1, max_chunk=16, keep_layers=False):
     from zgml_b200.host.lududra import LududraConfig, LududraModel
     from zgml_b200.host.session import SequenceSession
     model = LududraModel(be, LududraConfig.from_dict(cfg), lambda n: W[n], dtype)
@@ -57,8 +62,8 @@ def test_mixer_alone(cuda_backend, layer, dtype):
     toks = tokens(cfg, 45)
     want, stream = ref.forward(cfg, as_f64(W), toks)
     s = open_model(cuda_backend, cfg, W, dtype, max_chunk=64, keep_layers=True)
-    got = s.feed("a", toks[:32] + toks[32:40] + toks[40:44] + toks[44:], range(45))
-    assert rel(got, want) < TOL
+    got = s.feed("a", toks, range(45))
+    assert rel(got, want) < tol(dtype)
     close(s)
 
 
@@ -102,8 +107,8 @@ def test_prefill_equals_token_by_token(cuda_backend, dtype):
     s = open_model(cuda_backend, MIXED, W, dtype, n_slots=2)
     whole = s.feed("whole", toks, range(40))
     single = np.concatenate([s.feed("single", [t], [0]) for t in toks])
-    assert rel(whole, want) < TOL and rel(single, want) < TOL
-    assert rel(whole[:3], want[:3]) < TOL   # the first tokens see zeros before the start, not a stale tail or ring
+    assert rel(whole, want) < tol(dtype) and rel(single, want) < TOL     # single tokens take the exact row kernels in both formats
+    assert rel(whole[:3], want[:3]) < tol(dtype)   # the first tokens see zeros before the start, not a stale tail or ring
     close(s)
 
 

@@ -203,6 +203,7 @@ SYMBOLS = [
     ("zg_cuda_comm_mode", C.c_int, [vp]),
     ("zg_cuda_trace", C.c_int, [vp, C.c_int]),
     ("zg_cuda_trace_read", sz, [vp, vp, sz]),
+    ("zg_cuda_seq_scratch_elems", sz, [C.POINTER(ZgOp)]),
     ("zg_cuda_malloc", vp, [vp, sz]),
     ("zg_cuda_free_device", None, [vp, vp]),
     ("zg_cuda_memcpy_h2d", C.c_int, [vp, vp, vp, sz]),

@@ -301,6 +301,11 @@ class ResidentQuantizedWeight:
         return q
 
 
+def seq_scratch_elems(op) -> int:
+    """f32 slots the scratch operand of a sequence-model op needs (zg_cuda_seq_scratch_elems)."""
+    return int(load_library().zg_cuda_seq_scratch_elems(C.byref(op)))
+
+
 class DeviceBuffer:
     """Caller-owned device memory (zg_cuda_malloc) that programs reference as an external buffer: dense weights and
     per-sequence state shared by the programs of one session.  `elems` counts f32 slots."""

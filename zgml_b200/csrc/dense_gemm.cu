@@ -55,6 +55,10 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                  ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
 }
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t c0, uint32_t c1, uint32_t c2, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                 ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar) : "memory");
+}
 // K-major, 128-byte swizzle, 8-row groups 1024 B apart
 __device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
     uint64_t d = 0;
@@ -83,10 +87,19 @@ struct GemmParams {
     float* out;
     const __nv_bfloat16* bias;
     uint32_t M, N, K, out_rs, out_vec4;
+    const int* tile_group;   // GROUPED: weight matrix (third TMA coordinate) of every 128-row tile, -1: tile unused
 };
 
+// GROUPED: the rows are sorted by weight matrix (expert) in whole 128-row tiles; tile t multiplies with matrix tile_group[t]
+// of the stacked [groups][N][K] weight tensor.
+template <bool GROUPED>
 __global__ void __launch_bounds__(kThreads, 1)
 dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+    int group = 0;
+    if (GROUPED) {
+        group = p.tile_group[blockIdx.y];
+        if (group < 0) return;   // uniform over the CTA, before any barrier or TMEM allocation
+    }
     extern __shared__ uint8_t dsm_raw[];
     const uint32_t base = (smem_u32(dsm_raw) + 1023u) & ~1023u;
     const uint32_t bars = base + kStages * kStage;
@@ -117,7 +130,8 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 if (!mbar_wait(empty + 8 * s, ph ^ 1)) break;
                 mbar_expect_tx(full + 8 * s, kStage);
                 tma_load_2d(base + s * kStage, &tmap_a, kt * BK, tile_m * BM, full + 8 * s);
-                tma_load_2d(base + s * kStage + kTileA, &tmap_b, kt * BK, tile_n * BN, full + 8 * s);
+                if (GROUPED) tma_load_3d(base + s * kStage + kTileA, &tmap_b, kt * BK, tile_n * BN, (uint32_t)group, full + 8 * s);
+                else tma_load_2d(base + s * kStage + kTileA, &tmap_b, kt * BK, tile_n * BN, full + 8 * s);
             }
         }
     } else if (warp == 1) {
@@ -213,7 +227,8 @@ bool prepare() {
         g_encode = (EncodeTiledFn)fn;
     }
     if (!g_attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(dense_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem);
+        cudaError_t e = cudaFuncSetAttribute(dense_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(dense_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem);
         if (e != cudaSuccess) { zg_set_error("cudaFuncSetAttribute(dense_gemm) failed: %s", cudaGetErrorString(e)); return false; }
         g_attr_set = true;
     }
@@ -224,7 +239,7 @@ bool prepare() {
 
 // The tensor path takes whole-tile-sized problems whose weight rows TMA can address (16-byte aligned base and pitch).
 bool zg_dense_gemm_usable(const void* w_bf16, uint32_t M, uint32_t N, uint32_t K) {
-    return M > 8 && N >= 64 && K >= 64 && K % 8 == 0 && (reinterpret_cast<uintptr_t>(w_bf16) & 15) == 0;
+    return M > 8 && N >= 8 && K >= 64 && K % 8 == 0 && (reinterpret_cast<uintptr_t>(w_bf16) & 15) == 0;
 }
 // bf16 copy of the activations: [round_up(M, 128)][round_up(K, 64)], counted in f32 slots
 size_t zg_dense_gemm_scratch_elems(uint32_t M, uint32_t K) {
@@ -264,10 +279,45 @@ bool zg_dense_gemm_launch(const void* w_bf16, const void* bias_bf16, const float
     GemmParams p;
     p.out = dst; p.bias = reinterpret_cast<const __nv_bfloat16*>(bias_bf16); p.M = M; p.N = N; p.K = K; p.out_rs = dst_rs;
     p.out_vec4 = ((reinterpret_cast<uintptr_t>(dst) & 15) == 0 && (dst_rs & 3) == 0) ? 1u : 0u;
+    p.tile_group = nullptr;
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-    dense_gemm_kernel<<<grid, kThreads, kSmem, st>>>(map_a, map_b, p);
+    dense_gemm_kernel<false><<<grid, kThreads, kSmem, st>>>(map_a, map_b, p);
     ZG_COUNT_LAUNCH();
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) { zg_set_error("dense gemm launch failed: %s", cudaGetErrorString(e)); return false; }
+    return true;
+}
+
+// Grouped form: xb = bf16 rows [rows][Kp] already sorted by group in whole 128-row tiles (rows % 128 == 0, Kp % 64 == 0, zero
+// padding), W = [groups][N][K] bfloat16, dst[rows][N] f32.  d_tile_group[rows / 128] selects the matrix of every tile (< 0: skip).
+bool zg_dense_gemm_grouped_launch(const void* w_bf16, uint32_t groups, const void* xb, uint32_t rows, uint32_t Kp, const int* d_tile_group, float* dst,
+                                  uint32_t N, uint32_t K, uint32_t dst_rs, cudaStream_t st) {
+    if (!prepare()) return false;
+    CUtensorMap map_a, map_b;
+    {
+        const cuuint64_t gdim[2] = {Kp, rows};
+        const cuuint64_t gstride[1] = {(cuuint64_t)Kp * 2};
+        const cuuint32_t box[2] = {BK, BM}, estr[2] = {1, 1};
+        CUresult r = g_encode(&map_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(xb), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) { zg_set_error("cuTensorMapEncodeTiled(grouped rows) failed (%d)", (int)r); return false; }
+    }
+    {
+        const cuuint64_t gdim[3] = {K, N, groups};
+        const cuuint64_t gstride[2] = {(cuuint64_t)K * 2, (cuuint64_t)N * K * 2};
+        const cuuint32_t box[3] = {BK, BN, 1}, estr[3] = {1, 1, 1};
+        CUresult r = g_encode(&map_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(w_bf16), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) { zg_set_error("cuTensorMapEncodeTiled(stacked weights) failed (%d)", (int)r); return false; }
+    }
+    GemmParams p;
+    p.out = dst; p.bias = nullptr; p.M = rows; p.N = N; p.K = K; p.out_rs = dst_rs;
+    p.out_vec4 = ((reinterpret_cast<uintptr_t>(dst) & 15) == 0 && (dst_rs & 3) == 0) ? 1u : 0u;
+    p.tile_group = d_tile_group;
+    dim3 grid((N + BN - 1) / BN, rows / BM);
+    dense_gemm_kernel<true><<<grid, kThreads, kSmem, st>>>(map_a, map_b, p);
+    ZG_COUNT_LAUNCH();
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) { zg_set_error("grouped dense gemm launch failed: %s", cudaGetErrorString(e)); return false; }
     return true;
 }

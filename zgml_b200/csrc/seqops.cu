@@ -264,6 +264,108 @@ __global__ void k_window_attention(float* __restrict__ dst, const float* __restr
     }
 }
 
+// The kernel above is the fallback for head sizes that are not a multiple of 4.  This one: one CTA per (token, head), its
+// warps split the window; inside a warp LK lanes share a key (each holds 4 * CH channels of it as float4s, so a key row is
+// one coalesced read that serves the score AND — keys being the values — the weighted sum), 32 / LK keys per trip.  Every
+// lane group keeps its own running (max, sum, accumulator); groups and warps are merged at the end, where the sink joins.
+template <int CH>
+__global__ void k_window_attention_v(float* __restrict__ dst, const float* __restrict__ proj, const float* __restrict__ ring,
+                                     const float* __restrict__ bias, const float* __restrict__ ctl, uint32_t H, uint32_t G, uint32_t dim,
+                                     uint32_t LK, uint32_t proj_rs, uint32_t q_off, uint32_t g_off, uint32_t window, uint32_t R, float scale,
+                                     float cap) {
+    extern __shared__ float sm[];                      // [warps][4 + dim]: max, sum, two pad words (float4 alignment), accumulator
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    const uint32_t t = blockIdx.x / H, h = blockIdx.x % H, kv = h / (H / G);
+    const uint32_t pos0 = (uint32_t)ctl_word(ctl, ZG_CTL_POS), slot = (uint32_t)ctl_word(ctl, ZG_CTL_SLOT);
+    const uint32_t p = pos0 + t;
+    const uint32_t lo = p + 1 >= window ? p + 1 - window : 0;
+    const uint32_t KP = 32 / LK, sub = lane % LK, ks = lane / LK;
+    const float* qrow = proj + (size_t)t * proj_rs + q_off + (size_t)h * dim;
+    float4 q[CH], acc[CH];
+    bool valid[CH];
+#pragma unroll
+    for (int c = 0; c < CH; c++) {
+        const uint32_t ch = (c * LK + sub) * 4;
+        valid[c] = ch < dim;
+        q[c] = valid[c] ? *reinterpret_cast<const float4*>(qrow + ch) : make_float4(0, 0, 0, 0);
+        acc[c] = make_float4(0, 0, 0, 0);
+    }
+    const size_t width = (size_t)G * dim;
+    const float* base = ring + (size_t)slot * R * width + (size_t)kv * dim;
+    const uint32_t n_keys = p - lo + 1;
+    const uint32_t per = ((n_keys + nw - 1) / nw + KP - 1) / KP * KP;
+    const uint32_t j_begin = lo + warp * per, j_end = min(p + 1, j_begin + per);   // this warp's keys [j_begin, j_end)
+    float m = -INFINITY, l = 0.0f;
+    for (uint32_t j0 = j_begin; j0 < j_end; j0 += KP) {
+        const uint32_t j = j0 + ks;
+        const bool on = j < j_end;
+        const float* k = base + (size_t)(j % R) * width;
+        float4 kvv[CH];
+        float d = 0.0f;
+#pragma unroll
+        for (int c = 0; c < CH; c++) {
+            kvv[c] = (on && valid[c]) ? *reinterpret_cast<const float4*>(k + (c * LK + sub) * 4) : make_float4(0, 0, 0, 0);
+            d = fmaf(q[c].x, kvv[c].x, fmaf(q[c].y, kvv[c].y, fmaf(q[c].z, kvv[c].z, fmaf(q[c].w, kvv[c].w, d))));
+        }
+        for (uint32_t o = LK >> 1; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+        if (on) {
+            float sc = d * scale;
+            if (cap > 0.0f) sc = cap * tanhf(sc / cap);
+            sc += bias[(size_t)(p - j) * H + h];
+            if (sc > m) {
+                const float corr = expf(m - sc);        // exp(-inf) = 0 on the first key
+                l *= corr;
+#pragma unroll
+                for (int c = 0; c < CH; c++) { acc[c].x *= corr; acc[c].y *= corr; acc[c].z *= corr; acc[c].w *= corr; }
+                m = sc;
+            }
+            const float pj = expf(sc - m);
+            l += pj;
+#pragma unroll
+            for (int c = 0; c < CH; c++) {
+                acc[c].x = fmaf(pj, kvv[c].x, acc[c].x); acc[c].y = fmaf(pj, kvv[c].y, acc[c].y);
+                acc[c].z = fmaf(pj, kvv[c].z, acc[c].z); acc[c].w = fmaf(pj, kvv[c].w, acc[c].w);
+            }
+        }
+    }
+    // merge the key slots of the warp (lanes that differ in lane / LK)
+    for (uint32_t o = LK; o < 32; o <<= 1) {
+        const float m2 = __shfl_xor_sync(0xffffffffu, m, o), l2 = __shfl_xor_sync(0xffffffffu, l, o);
+        const float M = fmaxf(m, m2);
+        const float w1 = m == -INFINITY ? 0.0f : expf(m - M), w2 = m2 == -INFINITY ? 0.0f : expf(m2 - M);
+        l = l * w1 + l2 * w2;
+#pragma unroll
+        for (int c = 0; c < CH; c++) {
+            acc[c].x = acc[c].x * w1 + __shfl_xor_sync(0xffffffffu, acc[c].x, o) * w2;
+            acc[c].y = acc[c].y * w1 + __shfl_xor_sync(0xffffffffu, acc[c].y, o) * w2;
+            acc[c].z = acc[c].z * w1 + __shfl_xor_sync(0xffffffffu, acc[c].z, o) * w2;
+            acc[c].w = acc[c].w * w1 + __shfl_xor_sync(0xffffffffu, acc[c].w, o) * w2;
+        }
+        m = M;
+    }
+    float* mine = sm + warp * (4 + dim);
+    if (lane < LK) {
+        if (sub == 0) { mine[0] = m; mine[1] = l; }
+#pragma unroll
+        for (int c = 0; c < CH; c++)
+            if (valid[c]) *reinterpret_cast<float4*>(mine + 4 + (c * LK + sub) * 4) = acc[c];
+    }
+    __syncthreads();
+    // merge the warps; the sink (score 0, no value) joins the denominator here
+    float M = 0.0f;
+    for (uint32_t w = 0; w < nw; w++) M = fmaxf(M, sm[w * (4 + dim)]);
+    float L = expf(-M);
+    for (uint32_t w = 0; w < nw; w++) { const float mw = sm[w * (4 + dim)]; if (mw != -INFINITY) L += sm[w * (4 + dim) + 1] * expf(mw - M); }
+    const float inv = 1.0f / L;
+    const float* grow = proj + (size_t)t * proj_rs + g_off + (size_t)h * dim;
+    float* out = dst + ((size_t)t * H + h) * dim;
+    for (uint32_t c = threadIdx.x; c < dim; c += blockDim.x) {
+        float a = 0.0f;
+        for (uint32_t w = 0; w < nw; w++) { const float mw = sm[w * (4 + dim)]; if (mw != -INFINITY) a = fmaf(sm[w * (4 + dim) + 4 + c], expf(mw - M), a); }
+        out[c] = a * inv * sigmoidf_(grow[c]);
+    }
+}
+
 // ── CAUSAL_CONV ──────────────────────────────────────────────────────────────────────────────────────────────────
 template <typename WT>
 __global__ void k_causal_conv(float* __restrict__ dst, const float* __restrict__ src, const WT* __restrict__ w, const float* __restrict__ state,
@@ -471,6 +573,106 @@ __global__ void k_moe_down(float* __restrict__ dst, const float* __restrict__ sr
     if (lane == 0) dst[(size_t)t * D + d] = acc;
 }
 
+// ── MOE_FFN, grouped form (prefill on bfloat16 sessions): the step's (token, choice) pairs are sorted by expert into whole
+// 128-row tiles, the rows are gathered as bf16, and every expert's gate / up / down products run as tiles of ONE grouped
+// tensor-core matmul each (dense_gemm.cu), so an expert's weights are read once per 128 rows instead of once per token ──
+struct MoeLayout {          // offsets in f32 slots inside the op's scratch operand
+    uint32_t R, Dp, Fp;     // rows incl. per-expert padding, padded widths of the bf16 copies
+    size_t tile_group, row_pair, pos_of_pair, xs, g, u, yb, z, total;
+};
+__host__ __device__ inline size_t up4(size_t n) { return (n + 3) & ~(size_t)3; }
+MoeLayout moe_layout(uint32_t T, uint32_t D, uint32_t ff, uint32_t E, uint32_t top) {
+    MoeLayout L;
+    L.R = (T * top + 127) / 128 * 128 + E * 128;
+    L.Dp = (D + 63) / 64 * 64; L.Fp = (ff + 63) / 64 * 64;
+    size_t o = 0;
+    L.tile_group = o; o = up4(o + L.R / 128);
+    L.row_pair = o; o = up4(o + L.R);
+    L.pos_of_pair = o; o = up4(o + (size_t)T * top);
+    L.xs = o; o = up4(o + (size_t)L.R * L.Dp / 2);
+    L.g = o; o = up4(o + (size_t)L.R * ff);
+    L.u = o; o = up4(o + (size_t)L.R * ff);
+    L.yb = o; o = up4(o + (size_t)L.R * L.Fp / 2);
+    L.z = o; o = up4(o + (size_t)L.R * D);
+    L.total = o;
+    return L;
+}
+constexpr uint32_t kMoeMaxExperts = 1024;
+__global__ void __launch_bounds__(1024) k_moe_sort(const float* __restrict__ route, int* __restrict__ tile_group, int* __restrict__ row_pair,
+                                                   int* __restrict__ pos_of_pair, uint32_t pairs, uint32_t E, uint32_t R) {
+    __shared__ int cnt[kMoeMaxExperts], off[kMoeMaxExperts + 1];
+    for (uint32_t e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
+    for (uint32_t r = threadIdx.x; r < R; r += blockDim.x) row_pair[r] = -1;
+    __syncthreads();
+    for (uint32_t i = threadIdx.x; i < pairs; i += blockDim.x) {
+        const uint32_t e = (uint32_t)reinterpret_cast<const int*>(route)[2 * (size_t)i];
+        if (e < E) atomicAdd(&cnt[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int o = 0;
+        for (uint32_t e = 0; e < E; e++) {
+            off[e] = o;
+            const int tiles = (cnt[e] + 127) / 128;
+            for (int t = 0; t < tiles; t++) tile_group[o / 128 + t] = (int)e;
+            o += tiles * 128;
+            cnt[e] = 0;                                  // becomes the expert's fill cursor
+        }
+        for (uint32_t t = (uint32_t)o / 128; t < R / 128; t++) tile_group[t] = -1;
+    }
+    __syncthreads();
+    for (uint32_t i = threadIdx.x; i < pairs; i += blockDim.x) {
+        const uint32_t e = (uint32_t)reinterpret_cast<const int*>(route)[2 * (size_t)i];
+        int pos = -1;
+        if (e < E) { pos = off[e] + atomicAdd(&cnt[e], 1); row_pair[pos] = (int)i; }
+        pos_of_pair[i] = pos;                            // which row a pair landed in does not change its result
+    }
+}
+__global__ void k_moe_gather(uint32_t* __restrict__ xs, const float* __restrict__ src, const int* __restrict__ row_pair, uint32_t D, uint32_t dp2,
+                             uint32_t top) {
+    const uint32_t r = blockIdx.x;
+    const int pair = row_pair[r];
+    const float* x = pair >= 0 ? src + (size_t)((uint32_t)pair / top) * D : nullptr;
+    for (uint32_t k2 = threadIdx.x; k2 < dp2; k2 += blockDim.x) {
+        const uint32_t k = 2 * k2;
+        const float a = (x && k < D) ? x[k] : 0.0f, b = (x && k + 1 < D) ? x[k + 1] : 0.0f;
+        uint32_t v;
+        asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(v) : "f"(b), "f"(a));
+        xs[(size_t)r * dp2 + k2] = v;
+    }
+}
+__global__ void k_moe_act(uint32_t* __restrict__ yb, const float* __restrict__ g, const float* __restrict__ u, const int* __restrict__ row_pair,
+                          uint32_t ff, uint32_t fp2, float limit, float alpha) {
+    const uint32_t r = blockIdx.x;
+    const bool live = row_pair[r] >= 0;
+    for (uint32_t f2 = threadIdx.x; f2 < fp2; f2 += blockDim.x) {
+        float y[2] = {0.0f, 0.0f};
+        for (int i = 0; i < 2; i++) {
+            const uint32_t f = 2 * f2 + i;
+            if (live && f < ff) {
+                const float gv = fminf(g[(size_t)r * ff + f], limit), uv = fminf(fmaxf(u[(size_t)r * ff + f], -limit), limit);
+                y[i] = gv * sigmoidf_(alpha * gv) * (uv + 1.0f);
+            }
+        }
+        uint32_t v;
+        asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(v) : "f"(y[1]), "f"(y[0]));
+        yb[(size_t)r * fp2 + f2] = v;
+    }
+}
+__global__ void k_moe_combine(float* __restrict__ dst, const float* __restrict__ src, const float* __restrict__ z, const float* __restrict__ route,
+                              const int* __restrict__ pos_of_pair, uint32_t D, uint32_t top) {
+    const uint32_t t = blockIdx.x;
+    for (uint32_t d = threadIdx.x; d < D; d += blockDim.x) {
+        float acc = 0.0f;
+        for (uint32_t c = 0; c < top; c++) {
+            const size_t pair = (size_t)t * top + c;
+            const int pos = pos_of_pair[pair];
+            acc = fmaf(route[2 * pair + 1], pos >= 0 ? z[(size_t)pos * D + d] : src[(size_t)t * D + d], acc);
+        }
+        dst[(size_t)t * D + d] = acc;
+    }
+}
+
 template <typename WT> const WT* wptr(float* const* bufs, uint32_t b, uint32_t off) { return reinterpret_cast<const WT*>(bufs[b]) + off; }
 
 }  // namespace
@@ -486,6 +688,28 @@ template <typename WT> const WT* wptr(float* const* bufs, uint32_t b, uint32_t o
     do {                                                                              \
         if ((wdt) == ZG_W_BF16) { typedef bf16 WT; __VA_ARGS__; } else { typedef float WT; __VA_ARGS__; } \
     } while (0)
+
+static bool dense_gemm_enabled() {
+    static const bool enabled = [] { const char* e = getenv("ZG_DENSE_GEMM"); return !(e && e[0] == '0'); }();
+    return enabled;
+}
+// MOE_FFN on bfloat16 weights with enough (token, choice) pairs to fill tiles runs grouped on the tensor cores
+static bool moe_grouped(const ZgSeqOp& s, float* const* bufs) {
+    const uint32_t T = s.n[0], D = s.n[1], ff = s.n[2], E = s.n[3], top = s.n[4];
+    if (!dense_gemm_enabled() || s.n[5] != ZG_W_BF16 || !E || E > kMoeMaxExperts || T * top <= 16 || D < 64 || ff < 64 || D % 8 || ff % 8) return false;
+    if (!bufs) return true;
+    for (int i = 0; i < 3; i++) if (reinterpret_cast<uintptr_t>(wptr<bf16>(bufs, s.buf[3], s.off[i])) & 15) return false;
+    return true;
+}
+// f32 slots the op's own scratch operand (MOE_FFN buf[4]) must have; 0 for ops without one
+size_t zg_seq_op_operand_scratch(const ZgOp& op) {
+    if (op.tag != ZG_OP_MOE_FFN) return 0;
+    const ZgSeqOp& s = op.u.seq;
+    size_t n = (size_t)s.n[0] * s.n[4] * s.n[2];
+    if (moe_grouped(s, nullptr)) { const size_t g = moe_layout(s.n[0], s.n[1], s.n[2], s.n[3], s.n[4]).total; if (g > n) n = g; }
+    return n ? n : 1;
+}
+extern "C" __attribute__((visibility("default"))) size_t zg_cuda_seq_scratch_elems(const ZgOp* op) { return op ? zg_seq_op_operand_scratch(*op) : 0; }
 
 uint32_t zg_delta_row_slices(uint32_t dim) {
     uint32_t rs = 1;
@@ -560,7 +784,7 @@ bool zg_seq_op_valid(const ZgOp& op, const size_t* elems, size_t n_bufs, char* w
         case ZG_OP_MOE_FFN: {
             const size_t T = s.n[0], D = s.n[1], ff = s.n[2], E = s.n[3], top = s.n[4];
             if (!T || !D || !top) return fail("moe_ffn: shape");
-            if (!fits(0, 0, T * D) || !fits(1, 0, T * D) || !fits(2, 0, T * top * 2) || !fits(4, 0, T * top * ff) ||
+            if (!fits(0, 0, T * D) || !fits(1, 0, T * D) || !fits(2, 0, T * top * 2) || !fits(4, 0, zg_seq_op_operand_scratch(op)) ||
                 (E && (!wfits(3, s.off[0], E * ff * D) || !wfits(3, s.off[1], E * ff * D) || !wfits(3, s.off[2], E * ff * D))))
                 return fail("moe_ffn: extent");
             if (s.buf[0] == s.buf[1]) return fail("moe_ffn: in place");
@@ -584,8 +808,7 @@ uint32_t zg_seq_op_writes(uint32_t tag) {
 // f32 slots of the shared activation scratch this op needs (0: none): a LINEAR over bfloat16 weights with more rows than the
 // row kernels take runs on the tensor cores (dense_gemm.cu) from a bf16 copy of its input.  ZG_DENSE_GEMM=0 keeps the exact tile.
 size_t zg_seq_op_scratch_elems(const ZgOp& op, float* const* bufs) {
-    static const bool enabled = [] { const char* e = getenv("ZG_DENSE_GEMM"); return !(e && e[0] == '0'); }();
-    if (!enabled || op.tag != ZG_OP_LINEAR || op.u.seq.n[5] != ZG_W_BF16) return 0;
+    if (!dense_gemm_enabled() || op.tag != ZG_OP_LINEAR || op.u.seq.n[5] != ZG_W_BF16) return 0;
     const ZgSeqOp& s = op.u.seq;
     if (!zg_dense_gemm_usable(wptr<bf16>(bufs, s.buf[2], s.off[0]), s.n[0], s.n[1], s.n[2])) return 0;
     return zg_dense_gemm_scratch_elems(s.n[0], s.n[2]);
@@ -636,9 +859,26 @@ bool zg_launch_seq_op(ZgCudaCtx* ctx, const ZgOp& op, float* const* bufs, float*
             const uint32_t T = s.n[0], H = s.n[1], G = s.n[2], dim = s.n[3];
             k_ring_append<<<T, 128, 0, st>>>(bufs[s.buf[2]], bufs[s.buf[1]], bufs[s.buf[4]], s.off[1], s.n[4], G * dim, s.n[6]);
             ZG_SEQ_CHECK();
-            const uint32_t warps = 4;
-            k_window_attention<<<(T * H + warps - 1) / warps, warps * 32, warps * dim * sizeof(float), st>>>(
-                bufs[s.buf[0]], bufs[s.buf[1]], bufs[s.buf[2]], bufs[s.buf[3]], bufs[s.buf[4]], T, H, G, dim, s.n[4], s.off[0], s.off[2], s.n[5], s.n[6], s.f[0], s.f[1]);
+            const size_t width = (size_t)G * dim;
+            const bool vec = dim % 4 == 0 && s.off[0] % 4 == 0 && s.n[4] % 4 == 0 && width % 4 == 0 && (reinterpret_cast<uintptr_t>(bufs[s.buf[1]]) & 15) == 0 &&
+                             (reinterpret_cast<uintptr_t>(bufs[s.buf[2]]) & 15) == 0;
+            if (vec) {
+                const uint32_t CH = dim > 128 ? 2 : 1;
+                uint32_t LK = 1;
+                while (LK * 4 * CH < dim) LK <<= 1;
+                const uint32_t nw = T * H <= 64 ? 16 : (T * H <= 1024 ? 8 : 4);
+                const size_t smem = (size_t)nw * (4 + dim) * sizeof(float);
+                if (CH == 1)
+                    k_window_attention_v<1><<<T * H, nw * 32, smem, st>>>(bufs[s.buf[0]], bufs[s.buf[1]], bufs[s.buf[2]], bufs[s.buf[3]], bufs[s.buf[4]], H, G, dim, LK,
+                                                                        s.n[4], s.off[0], s.off[2], s.n[5], s.n[6], s.f[0], s.f[1]);
+                else
+                    k_window_attention_v<2><<<T * H, nw * 32, smem, st>>>(bufs[s.buf[0]], bufs[s.buf[1]], bufs[s.buf[2]], bufs[s.buf[3]], bufs[s.buf[4]], H, G, dim, LK,
+                                                                        s.n[4], s.off[0], s.off[2], s.n[5], s.n[6], s.f[0], s.f[1]);
+            } else {
+                const uint32_t warps = 4;
+                k_window_attention<<<(T * H + warps - 1) / warps, warps * 32, warps * dim * sizeof(float), st>>>(
+                    bufs[s.buf[0]], bufs[s.buf[1]], bufs[s.buf[2]], bufs[s.buf[3]], bufs[s.buf[4]], T, H, G, dim, s.n[4], s.off[0], s.off[2], s.n[5], s.n[6], s.f[0], s.f[1]);
+            }
             ZG_SEQ_CHECK();
             return true;
         }
@@ -681,6 +921,25 @@ bool zg_launch_seq_op(ZgCudaCtx* ctx, const ZgOp& op, float* const* bufs, float*
         }
         case ZG_OP_MOE_FFN: {
             const uint32_t T = s.n[0], D = s.n[1], ff = s.n[2], E = s.n[3], top = s.n[4];
+            if (moe_grouped(s, bufs)) {
+                const MoeLayout L = moe_layout(T, D, ff, E, top);
+                float* sc = bufs[s.buf[4]];
+                int* tile_group = reinterpret_cast<int*>(sc + L.tile_group);
+                int* row_pair = reinterpret_cast<int*>(sc + L.row_pair);
+                int* pos_of_pair = reinterpret_cast<int*>(sc + L.pos_of_pair);
+                k_moe_sort<<<1, 1024, 0, st>>>(bufs[s.buf[2]], tile_group, row_pair, pos_of_pair, T * top, E, L.R);
+                ZG_SEQ_CHECK();
+                k_moe_gather<<<L.R, 256, 0, st>>>(reinterpret_cast<uint32_t*>(sc + L.xs), bufs[s.buf[1]], row_pair, D, L.Dp / 2, top);
+                ZG_SEQ_CHECK();
+                if (!zg_dense_gemm_grouped_launch(wptr<bf16>(bufs, s.buf[3], s.off[0]), E, sc + L.xs, L.R, L.Dp, tile_group, sc + L.g, ff, D, ff, st) ||
+                    !zg_dense_gemm_grouped_launch(wptr<bf16>(bufs, s.buf[3], s.off[1]), E, sc + L.xs, L.R, L.Dp, tile_group, sc + L.u, ff, D, ff, st)) return false;
+                k_moe_act<<<L.R, 256, 0, st>>>(reinterpret_cast<uint32_t*>(sc + L.yb), sc + L.g, sc + L.u, row_pair, ff, L.Fp / 2, s.f[0], s.f[1]);
+                ZG_SEQ_CHECK();
+                if (!zg_dense_gemm_grouped_launch(wptr<bf16>(bufs, s.buf[3], s.off[2]), E, sc + L.yb, L.R, L.Fp, tile_group, sc + L.z, D, ff, D, st)) return false;
+                k_moe_combine<<<T, 256, 0, st>>>(bufs[s.buf[0]], bufs[s.buf[1]], sc + L.z, bufs[s.buf[2]], pos_of_pair, D, top);
+                ZG_SEQ_CHECK();
+                return true;
+            }
             ZG_SEQ_WDT(s.n[5], {
                 if (E && ff) {
                     k_moe_up<WT><<<dim3((ff + 7) / 8, T * top), 256, 0, st>>>(bufs[s.buf[4]], bufs[s.buf[1]], bufs[s.buf[2]], wptr<WT>(bufs, s.buf[3], s.off[0]),

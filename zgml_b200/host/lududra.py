@@ -26,7 +26,7 @@ from typing import Dict, List, Optional
 import numpy as np
 
 from .. import abi
-from ..backend import CudaBackend, DeviceBuffer, DeviceOp, DeviceProgram, ExternBuffer, ProgramIO
+from ..backend import CudaBackend, DeviceBuffer, DeviceOp, DeviceProgram, ExternBuffer, ProgramIO, seq_scratch_elems
 from .safetensors import SafetensorsFile, f32_to_bf16_bits
 from .session import LoweredProgram
 from .state import SequenceStatePool, StateSpec
@@ -306,9 +306,10 @@ class LududraModel:
                 rl, rt = scratch("router", T * NE), scratch("route", T * top * 2)
                 ops.append(DeviceOp.linear(rl, h, wb, A.off["router"], T, NE, D, wdt))
                 ops.append(DeviceOp.route(rt, rl, wb, A.off["correction"], T, NE, top, wdt))
-                ys = scratch("expert", T * top * ff)
-                ops.append(DeviceOp.moe_ffn(y, h, rt, wb, ys, A.off["gate"], A.off["up"], A.off["down"], T, D, ff, E, top, wdt,
-                                            meta["limit"], EXPERT_ALPHA))
+                moe_op = DeviceOp.moe_ffn(y, h, rt, wb, 0, A.off["gate"], A.off["up"], A.off["down"], T, D, ff, E, top, wdt,
+                                          meta["limit"], EXPERT_ALPHA)
+                moe_op.u.seq.buf[4] = scratch("expert", seq_scratch_elems(moe_op))   # the library knows what its kernels stage
+                ops.append(moe_op)
                 nx = next_x(x)
                 ops.append(DeviceOp.norm(nx, y, wb, A.off["norm2b"], T, D, eps, wdt, res=x))
                 x = nx
@@ -326,3 +327,63 @@ class LududraModel:
         for b in self.buffers:
             b.free()
         self.buffers = []
+
+
+def synthetic_config(width: int, n_layers: int, heads: int, kv_heads: int, dim: int, window: int, experts: int, top: int, ff: int,
+                     vocab: int, identity: int = 1, attention_every: int = 2, conv: int = 4) -> dict:
+    """config.json contents of a random-init model: every `attention_every`-th layer is a window-attention layer, the
+    others are delta-rule layers; each has a routed feed-forward."""
+    layers = []
+    for i in range(n_layers):
+        mlp = {"kind": "moe", "expert": {"ff": ff, "limit": 7.0}, "router": {"experts": experts, "identity": identity, "top": top}}
+        if i % attention_every == attention_every - 1:
+            mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "mask": {"size": window}, "bias_max": 4 * window,
+                     "softcap": 50.0, "scale": dim ** -0.5}
+            layers.append({"type": "attention", "mixer": mixer, "mlp": mlp})
+        else:
+            layers.append({"type": "channel_delta", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "conv": conv}, "mlp": mlp})
+    return {"architecture": ARCHITECTURE, "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0}, "layers": layers}
+
+
+def synthetic_tensors(cfg: dict, seed: int = 0, rank: int = 64, rel_rows: int = 32):
+    """Accessor name -> random f32 tensor of the shape the configuration implies (benchmarks and smoke runs; values are
+    scaled like a trained model's so that activations stay O(1))."""
+    D = cfg["width"]
+
+    def shape_of(name):
+        if name in ("embed", "head"):
+            return (cfg["vocab"], D)
+        if name == "final.norm":
+            return (D,)
+        layer, rest = name.split(".", 1)
+        L = cfg["layers"][int(layer[1:])]
+        m = L["mixer"]
+        H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+        if rest.startswith("norm"):
+            return (D,)
+        if rest.startswith("mlp."):
+            r, ff = L["mlp"]["router"], L["mlp"]["expert"]["ff"]
+            part = rest.split(".")[-1]
+            return {"router": (r["experts"] + r["identity"], D), "correction": (r["experts"] + r["identity"],), "gate": (ff, D), "up": (ff, D),
+                    "down": (D, ff)}[part]
+        t = rest[len("mix."):]
+        if L["type"] == "attention":
+            return {"q": (H * d, D), "q.b": (H * d,), "k": (G * d, D), "k.b": (G * d,), "rel": (rel_rows, H), "g": (H * dv, D), "o": (D, H * dv)}[t]
+        return {"q": (G * d, D), "k": (G * d, D), "v": (H * dv, D), "q.conv": (G * d, m["conv"]), "k.conv": (G * d, m["conv"]),
+                "v.conv": (H * dv, m["conv"]), "b": (H, D), "A_log": (H,), "norm": (dv,), "a1": (rank, D), "a2": (H * d, rank),
+                "dt_bias": (H * d,), "g1": (rank, D), "g2": (H * dv, rank), "o": (D, H * dv)}[t]
+
+    def get(name):
+        import zlib
+        shp = shape_of(name)
+        r = np.random.default_rng([seed, zlib.crc32(name.encode())])
+        if name.endswith(("norm", "norm1", "norm2", "norm1b", "norm2b")):
+            return np.ones(shp, np.float32)
+        if len(shp) == 1:
+            return (r.random(shp, dtype=np.float32) - 0.5) * 0.2
+        a = r.random(shp, dtype=np.float32)
+        a -= 0.5
+        a *= np.float32(np.sqrt(12.0 / shp[1]))
+        return a
+
+    return get
