@@ -263,3 +263,16 @@ def test_tensor_core_prefill_of_a_wide_model(cuda_backend):
     assert rel(g32, want) < TOL
     assert rel(g16, want) < 3e-2
     close(s16), close(s32)
+
+
+def test_long_window_decode_splits_the_window(cuda_backend):
+    """A window long enough that single-token steps spread it over several CTAs (partial softmax states merged afterwards):
+    decoding across the point where the window fills up, against the prompt path and the restatement."""
+    cfg = config([attention_layer(heads=2, kv_heads=1, dim=16, window=160, rel_rows=12, bias_max=200, softcap=20.0)], width=32, vocab=50)
+    W = random_weights(cfg, seed=31, qk_gain=6.0)
+    toks = tokens(cfg, 200)
+    want, _ = ref.forward(cfg, as_f64(W), toks)
+    s = open_model(cuda_backend, cfg, W, max_chunk=64)
+    got = [s.feed("r", toks[:130], range(130))] + [s.feed("r", [t], [0]) for t in toks[130:]]
+    assert rel(np.concatenate(got), want) < TOL
+    close(s)

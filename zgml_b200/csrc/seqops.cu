@@ -40,6 +40,23 @@ __device__ float block_sum(float v, float* sh) {
     for (int i = 0; i < nw; i++) r += sh[i];
     return r;
 }
+// Programmatic dependent launch (as the framework's other program kernels do): let the next kernel of the stream become
+// resident while this one runs, and hold this one until its predecessor has completed.  Nothing is read before the wait.
+__device__ __forceinline__ void pdl_enter() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+template <typename... KArgs, typename... Args>
+inline void launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_zg_pdl ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
 __device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf(-z)); }
 __device__ __forceinline__ float softplusf_(float z) { return z > 20.0f ? z : log1pf(expf(z)); }
 __device__ __forceinline__ int ctl_word(const float* ctl, int i) { return reinterpret_cast<const int*>(ctl)[i]; }
@@ -47,6 +64,7 @@ __device__ __forceinline__ int ctl_word(const float* ctl, int i) { return reinte
 // ── EMBED ─────────────────────────────────────────────────────────────────────────────────────────────────────────
 template <typename WT>
 __global__ void k_embed(float* __restrict__ dst, const float* __restrict__ ctl, const WT* __restrict__ table, uint32_t D, float scale) {
+    pdl_enter();
     const uint32_t t = blockIdx.x;
     const size_t row = (size_t)ctl_word(ctl, ZG_CTL_IDS + t) * D;
     for (uint32_t c = threadIdx.x; c < D; c += blockDim.x) dst[(size_t)t * D + c] = wld(table, row + c) * scale;
@@ -57,6 +75,7 @@ constexpr int kGemvRows = 8;
 template <typename WT>
 __global__ void k_linear_rows(float* __restrict__ dst, const float* __restrict__ src, const WT* __restrict__ W, const WT* __restrict__ bias,
                               uint32_t M, uint32_t N, uint32_t K, uint32_t src_rs, uint32_t dst_rs) {
+    pdl_enter();
     const uint32_t n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (n >= N) return;
     const WT* w = W + (size_t)n * K;
@@ -94,27 +113,47 @@ template <> __device__ __forceinline__ void wld_vec<float>(const float* p, float
     const float4 v = *reinterpret_cast<const float4*>(p);
     out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
 }
+// The activation rows are staged once per CTA in shared memory (float4 reads, no per-weight global loads); two weight
+// vectors per lane are in flight per trip.
 template <typename WT, int MR>
 __global__ void k_linear_rows_vec(float* __restrict__ dst, const float* __restrict__ src, const WT* __restrict__ W, const WT* __restrict__ bias,
                                   uint32_t M, uint32_t N, uint32_t K, uint32_t src_rs, uint32_t dst_rs) {
+    pdl_enter();
     constexpr int V = WVec<WT>::n;
+    extern __shared__ float xs[];                      // [M][K]
+    for (uint32_t e = threadIdx.x; e < M * K; e += blockDim.x) xs[e] = src[(size_t)(e / K) * src_rs + e % K];
+    __syncthreads();
     const uint32_t n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (n >= N) return;
     const WT* w = W + (size_t)n * K;
     float acc[MR];
 #pragma unroll
     for (int m = 0; m < MR; m++) acc[m] = 0.0f;
-    for (uint32_t k = lane * V; k < K; k += 32 * V) {
-        float wv[V];
-        wld_vec<WT>(w + k, wv);
+    auto fma_vec = [&](const float* wv, uint32_t k) {
 #pragma unroll
         for (int m = 0; m < MR; m++) {
             if (m < (int)M) {
-                const float* x = src + (size_t)m * src_rs + k;
+                const float4* x = reinterpret_cast<const float4*>(xs + (size_t)m * K + k);
 #pragma unroll
-                for (int i = 0; i < V; i++) acc[m] = fmaf(x[i], wv[i], acc[m]);
+                for (int i = 0; i < V / 4; i++) {
+                    const float4 xv = x[i];
+                    acc[m] = fmaf(xv.x, wv[4 * i], fmaf(xv.y, wv[4 * i + 1], fmaf(xv.z, wv[4 * i + 2], fmaf(xv.w, wv[4 * i + 3], acc[m]))));
+                }
             }
         }
+    };
+    uint32_t k = lane * V;
+    for (; k + 32 * V < K; k += 64 * V) {
+        float w0[V], w1[V];
+        wld_vec<WT>(w + k, w0);
+        wld_vec<WT>(w + k + 32 * V, w1);
+        fma_vec(w0, k);
+        fma_vec(w1, k + 32 * V);
+    }
+    if (k < K) {
+        float w0[V];
+        wld_vec<WT>(w + k, w0);
+        fma_vec(w0, k);
     }
     const float b = bias ? wld(bias, n) : 0.0f;
 #pragma unroll
@@ -171,30 +210,58 @@ __global__ void __launch_bounds__(256) k_linear_tile(float* __restrict__ dst, co
 }
 
 // ── NORM: one CTA per row ────────────────────────────────────────────────────────────────────────────────────────
+constexpr int kNormCache = 16;   // values a thread keeps: rows up to 16 x blockDim are read from memory once
 template <typename WT>
 __global__ void k_norm(float* __restrict__ dst, const float* __restrict__ src, const WT* __restrict__ w, const float* __restrict__ res,
                        uint32_t cols, uint32_t kind, float eps) {
+    pdl_enter();
     __shared__ float sh[32];
     const size_t row = (size_t)blockIdx.x * cols;
     const float* x = src + row;
-    float mean = 0.0f;
-    if (kind == 0) {
-        float s = 0.0f;
+    const bool cached = cols <= kNormCache * blockDim.x;
+    float v[kNormCache];
+    float s = 0.0f;
+    if (cached) {
+#pragma unroll
+        for (int i = 0; i < kNormCache; i++) {
+            const uint32_t c = threadIdx.x + i * blockDim.x;
+            v[i] = c < cols ? x[c] : 0.0f;
+            s += v[i];
+        }
+    } else {
         for (uint32_t c = threadIdx.x; c < cols; c += blockDim.x) s += x[c];
-        mean = block_sum(s, sh) / (float)cols;
     }
+    const float mean = kind == 0 ? block_sum(s, sh) / (float)cols : 0.0f;
     float q = 0.0f;
-    for (uint32_t c = threadIdx.x; c < cols; c += blockDim.x) { const float d = x[c] - mean; q = fmaf(d, d, q); }
+    if (cached) {
+#pragma unroll
+        for (int i = 0; i < kNormCache; i++) {
+            const uint32_t c = threadIdx.x + i * blockDim.x;
+            const float d = c < cols ? v[i] - mean : 0.0f;
+            q = fmaf(d, d, q);
+        }
+    } else {
+        for (uint32_t c = threadIdx.x; c < cols; c += blockDim.x) { const float d = x[c] - mean; q = fmaf(d, d, q); }
+    }
     const float inv = 1.0f / sqrtf(block_sum(q, sh) / (float)cols + eps);
-    for (uint32_t c = threadIdx.x; c < cols; c += blockDim.x) {
-        const float y = (x[c] - mean) * inv * wld(w, c);
-        dst[row + c] = res ? res[row + c] + y : y;
+    if (cached) {
+#pragma unroll
+        for (int i = 0; i < kNormCache; i++) {
+            const uint32_t c = threadIdx.x + i * blockDim.x;
+            if (c < cols) { const float y = (v[i] - mean) * inv * wld(w, c); dst[row + c] = res ? res[row + c] + y : y; }
+        }
+    } else {
+        for (uint32_t c = threadIdx.x; c < cols; c += blockDim.x) {
+            const float y = (x[c] - mean) * inv * wld(w, c);
+            dst[row + c] = res ? res[row + c] + y : y;
+        }
     }
 }
 
 // ── WINDOW_ATTENTION ─────────────────────────────────────────────────────────────────────────────────────────────
 __global__ void k_ring_append(float* __restrict__ ring, const float* __restrict__ proj, const float* __restrict__ ctl, uint32_t k_off,
                               uint32_t proj_rs, uint32_t width, uint32_t R) {
+    pdl_enter();
     const uint32_t t = blockIdx.x;
     const uint32_t pos = (uint32_t)ctl_word(ctl, ZG_CTL_POS) + t, slot = (uint32_t)ctl_word(ctl, ZG_CTL_SLOT);
     float* row = ring + ((size_t)slot * R + pos % R) * width;
@@ -207,6 +274,7 @@ __global__ void k_window_attention(float* __restrict__ dst, const float* __restr
                                    const float* __restrict__ bias, const float* __restrict__ ctl, uint32_t T, uint32_t H, uint32_t G,
                                    uint32_t dim, uint32_t proj_rs, uint32_t q_off, uint32_t g_off, uint32_t window, uint32_t R,
                                    float scale, float cap) {
+    pdl_enter();
     extern __shared__ float sq[];                      // [warps][dim]
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
     const uint32_t item = blockIdx.x * nw + warp;
@@ -272,7 +340,8 @@ template <int CH>
 __global__ void k_window_attention_v(float* __restrict__ dst, const float* __restrict__ proj, const float* __restrict__ ring,
                                      const float* __restrict__ bias, const float* __restrict__ ctl, uint32_t H, uint32_t G, uint32_t dim,
                                      uint32_t LK, uint32_t proj_rs, uint32_t q_off, uint32_t g_off, uint32_t window, uint32_t R, float scale,
-                                     float cap) {
+                                     float cap, float* __restrict__ part) {
+    pdl_enter();
     extern __shared__ float sm[];                      // [warps][4 + dim]: max, sum, two pad words (float4 alignment), accumulator
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
     const uint32_t t = blockIdx.x / H, h = blockIdx.x % H, kv = h / (H / G);
@@ -292,24 +361,43 @@ __global__ void k_window_attention_v(float* __restrict__ dst, const float* __res
     }
     const size_t width = (size_t)G * dim;
     const float* base = ring + (size_t)slot * R * width + (size_t)kv * dim;
+    // gridDim.y CTAs split the window (decode: few (token, head) pairs, long windows), the warps of a CTA split its share
     const uint32_t n_keys = p - lo + 1;
-    const uint32_t per = ((n_keys + nw - 1) / nw + KP - 1) / KP * KP;
-    const uint32_t j_begin = lo + warp * per, j_end = min(p + 1, j_begin + per);   // this warp's keys [j_begin, j_end)
+    const uint32_t per_cta = (n_keys + gridDim.y - 1) / gridDim.y;
+    const uint32_t c_begin = lo + blockIdx.y * per_cta, c_end = min(p + 1, c_begin + per_cta);
+    const uint32_t per = ((c_end > c_begin ? c_end - c_begin : 0) + nw - 1) / nw;
+    const uint32_t j_begin = c_begin + warp * per, j_end = min(c_end, j_begin + per);   // this warp's keys [j_begin, j_end)
     float m = -INFINITY, l = 0.0f;
-    for (uint32_t j0 = j_begin; j0 < j_end; j0 += KP) {
-        const uint32_t j = j0 + ks;
-        const bool on = j < j_end;
-        const float* k = base + (size_t)(j % R) * width;
-        float4 kvv[CH];
-        float d = 0.0f;
+    constexpr int U = 4;                               // keys in flight per lane group: their loads are issued together
+    for (uint32_t j0 = j_begin; j0 < j_end; j0 += KP * U) {
+        float4 kvv[U][CH];
+        float d[U];
+        bool on[U];
 #pragma unroll
-        for (int c = 0; c < CH; c++) {
-            kvv[c] = (on && valid[c]) ? *reinterpret_cast<const float4*>(k + (c * LK + sub) * 4) : make_float4(0, 0, 0, 0);
-            d = fmaf(q[c].x, kvv[c].x, fmaf(q[c].y, kvv[c].y, fmaf(q[c].z, kvv[c].z, fmaf(q[c].w, kvv[c].w, d))));
+        for (int u = 0; u < U; u++) {
+            const uint32_t j = j0 + u * KP + ks;
+            on[u] = j < j_end;
+            const float* k = base + (size_t)(j % R) * width;
+#pragma unroll
+            for (int c = 0; c < CH; c++)
+                kvv[u][c] = (on[u] && valid[c]) ? *reinterpret_cast<const float4*>(k + (c * LK + sub) * 4) : make_float4(0, 0, 0, 0);
         }
-        for (uint32_t o = LK >> 1; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
-        if (on) {
-            float sc = d * scale;
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            d[u] = 0.0f;
+#pragma unroll
+            for (int c = 0; c < CH; c++)
+                d[u] = fmaf(q[c].x, kvv[u][c].x, fmaf(q[c].y, kvv[u][c].y, fmaf(q[c].z, kvv[u][c].z, fmaf(q[c].w, kvv[u][c].w, d[u]))));
+        }
+        for (uint32_t o = LK >> 1; o > 0; o >>= 1) {
+#pragma unroll
+            for (int u = 0; u < U; u++) d[u] += __shfl_xor_sync(0xffffffffu, d[u], o);
+        }
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            if (!on[u]) continue;
+            const uint32_t j = j0 + u * KP + ks;
+            float sc = d[u] * scale;
             if (cap > 0.0f) sc = cap * tanhf(sc / cap);
             sc += bias[(size_t)(p - j) * H + h];
             if (sc > m) {
@@ -323,8 +411,8 @@ __global__ void k_window_attention_v(float* __restrict__ dst, const float* __res
             l += pj;
 #pragma unroll
             for (int c = 0; c < CH; c++) {
-                acc[c].x = fmaf(pj, kvv[c].x, acc[c].x); acc[c].y = fmaf(pj, kvv[c].y, acc[c].y);
-                acc[c].z = fmaf(pj, kvv[c].z, acc[c].z); acc[c].w = fmaf(pj, kvv[c].w, acc[c].w);
+                acc[c].x = fmaf(pj, kvv[u][c].x, acc[c].x); acc[c].y = fmaf(pj, kvv[u][c].y, acc[c].y);
+                acc[c].z = fmaf(pj, kvv[u][c].z, acc[c].z); acc[c].w = fmaf(pj, kvv[u][c].w, acc[c].w);
             }
         }
     }
@@ -351,18 +439,42 @@ __global__ void k_window_attention_v(float* __restrict__ dst, const float* __res
             if (valid[c]) *reinterpret_cast<float4*>(mine + 4 + (c * LK + sub) * 4) = acc[c];
     }
     __syncthreads();
-    // merge the warps; the sink (score 0, no value) joins the denominator here
-    float M = 0.0f;
+    // merge the warps
+    float M = -INFINITY;
     for (uint32_t w = 0; w < nw; w++) M = fmaxf(M, sm[w * (4 + dim)]);
-    float L = expf(-M);
+    float L = 0.0f;
     for (uint32_t w = 0; w < nw; w++) { const float mw = sm[w * (4 + dim)]; if (mw != -INFINITY) L += sm[w * (4 + dim) + 1] * expf(mw - M); }
-    const float inv = 1.0f / L;
     const float* grow = proj + (size_t)t * proj_rs + g_off + (size_t)h * dim;
     float* out = dst + ((size_t)t * H + h) * dim;
+    float* mine_part = part ? part + ((size_t)blockIdx.x * gridDim.y + blockIdx.y) * (4 + dim) : nullptr;
+    // the sink (score 0, no value) joins the denominator where the last merge happens
+    const float Ms = fmaxf(M, 0.0f);
+    const float wk = M == -INFINITY ? 0.0f : expf(M - Ms);
+    const float inv = 1.0f / (expf(-Ms) + L * wk);
+    if (mine_part && threadIdx.x == 0) { mine_part[0] = M; mine_part[1] = L; }
     for (uint32_t c = threadIdx.x; c < dim; c += blockDim.x) {
         float a = 0.0f;
         for (uint32_t w = 0; w < nw; w++) { const float mw = sm[w * (4 + dim)]; if (mw != -INFINITY) a = fmaf(sm[w * (4 + dim) + 4 + c], expf(mw - M), a); }
-        out[c] = a * inv * sigmoidf_(grow[c]);
+        if (mine_part) mine_part[4 + c] = a;
+        else out[c] = a * wk * inv * sigmoidf_(grow[c]);
+    }
+}
+// merge of the window shares of k_window_attention_v: one CTA per (token, head)
+__global__ void k_window_attention_merge(float* __restrict__ dst, const float* __restrict__ proj, const float* __restrict__ part, uint32_t H, uint32_t dim,
+                                         uint32_t S, uint32_t proj_rs, uint32_t g_off) {
+    pdl_enter();
+    const uint32_t t = blockIdx.x / H, h = blockIdx.x % H;
+    const float* P = part + (size_t)blockIdx.x * S * (4 + dim);
+    float M = 0.0f;                                    // the sink's score
+    for (uint32_t i = 0; i < S; i++) M = fmaxf(M, P[i * (4 + dim)]);
+    float L = expf(-M);
+    for (uint32_t i = 0; i < S; i++) { const float mi = P[i * (4 + dim)]; if (mi != -INFINITY) L += P[i * (4 + dim) + 1] * expf(mi - M); }
+    const float inv = 1.0f / L;
+    const float* grow = proj + (size_t)t * proj_rs + g_off + (size_t)h * dim;
+    for (uint32_t c = threadIdx.x; c < dim; c += blockDim.x) {
+        float a = 0.0f;
+        for (uint32_t i = 0; i < S; i++) { const float mi = P[i * (4 + dim)]; if (mi != -INFINITY) a = fmaf(P[i * (4 + dim) + 4 + c], expf(mi - M), a); }
+        dst[((size_t)t * H + h) * dim + c] = a * inv * sigmoidf_(grow[c]);
     }
 }
 
@@ -370,6 +482,7 @@ __global__ void k_window_attention_v(float* __restrict__ dst, const float* __res
 template <typename WT>
 __global__ void k_causal_conv(float* __restrict__ dst, const float* __restrict__ src, const WT* __restrict__ w, const float* __restrict__ state,
                               const float* __restrict__ ctl, uint32_t T, uint32_t C, uint32_t taps, uint32_t src_rs, uint32_t dst_rs, uint32_t act) {
+    pdl_enter();
     const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (e >= (size_t)T * C) return;
     const uint32_t t = (uint32_t)(e / C), c = (uint32_t)(e % C);
@@ -386,6 +499,7 @@ __global__ void k_causal_conv(float* __restrict__ dst, const float* __restrict__
 // state row r holds the input of time (first token of the NEXT step) - (taps - 1) + r; rows ascend, so shifting in place is safe
 __global__ void k_conv_advance(float* __restrict__ state, const float* __restrict__ src, const float* __restrict__ ctl, uint32_t T, uint32_t C,
                                uint32_t taps, uint32_t src_rs) {
+    pdl_enter();
     const uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= C) return;
     float* st = state + (size_t)ctl_word(ctl, ZG_CTL_SLOT) * (taps - 1) * C;
@@ -400,13 +514,14 @@ __global__ void k_conv_advance(float* __restrict__ state, const float* __restric
 // over CTAs.  A thread keeps kDeltaRows consecutive key rows of one column in registers; the RS threads of a column sit in
 // adjacent lanes and meet by shuffles.  The per-token vectors (unit k, scaled unit q, decay) of kDeltaTile tokens are
 // prepared by the whole CTA at once, then the tokens are walked without further barriers.
-constexpr int kDeltaRows = 16, kDeltaTile = 8, kDeltaThreads = 128;
+constexpr int kDeltaRows = 16, kDeltaTile = 16, kDeltaThreads = 128;
 template <typename WT>
 __global__ void __launch_bounds__(kDeltaThreads) k_delta_rule(
     float* __restrict__ dst, const float* __restrict__ qkv, const float* __restrict__ betab, const float* __restrict__ ab, const WT* __restrict__ wts,
     float* __restrict__ state, const float* __restrict__ ctl, uint32_t T, uint32_t H, uint32_t G, uint32_t dim, uint32_t vdim, uint32_t RS,
     uint32_t q_off, uint32_t k_off, uint32_t v_off, uint32_t beta_off, uint32_t A_off, uint32_t dt_off, uint32_t qkv_rs, uint32_t beta_rs,
     uint32_t a_rs, float unit_eps, float q_scale) {
+    pdl_enter();
     extern __shared__ float sm[];
     const uint32_t dpad = RS * kDeltaRows;             // rows incl. padding (k = q = 0, decay = 1 there)
     float* sk = sm;                                    // [tile][dpad]
@@ -447,13 +562,20 @@ __global__ void __launch_bounds__(kDeltaThreads) k_delta_rule(
             }
             if (lane == 0) sbeta[tt] = sigmoidf_(betab[(size_t)t * beta_rs + beta_off + h]);
         }
+        float vt[kDeltaTile];                              // the tile's values of this column: independent loads, issued together
+#pragma unroll
+        for (int tt = 0; tt < kDeltaTile; tt++)
+            vt[tt] = (live && (uint32_t)tt < nt) ? qkv[(size_t)(t0 + tt) * qkv_rs + v_off + (size_t)h * vdim + col] : 0.0f;
         __syncthreads();
-        for (uint32_t tt = 0; tt < nt; tt++) {
+#pragma unroll
+        for (int tti = 0; tti < kDeltaTile; tti++) {
+            const uint32_t tt = (uint32_t)tti;
+            if (tt >= nt) break;
             const uint32_t t = t0 + tt;
             const float* k = sk + tt * dpad + r * kDeltaRows;
             const float* q = sq + tt * dpad + r * kDeltaRows;
             const float* g = sg + tt * dpad + r * kDeltaRows;
-            const float v = live ? qkv[(size_t)t * qkv_rs + v_off + (size_t)h * vdim + col] : 0.0f;
+            const float v = vt[tti];
             float ks = 0.0f;
 #pragma unroll
             for (int i = 0; i < kDeltaRows; i++) { S[i] *= g[i]; ks = fmaf(S[i], k[i], ks); }
@@ -476,6 +598,7 @@ __global__ void __launch_bounds__(kDeltaThreads) k_delta_rule(
 template <typename WT>
 __global__ void k_delta_out(float* __restrict__ dst, const float* __restrict__ gate, const WT* __restrict__ wts, uint32_t TH, uint32_t H,
                             uint32_t vdim, uint32_t gate_rs, uint32_t nw_off, float eps) {
+    pdl_enter();
     const uint32_t item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (item >= TH) return;
     const uint32_t t = item / H, h = item % H;
@@ -491,6 +614,7 @@ __global__ void k_delta_out(float* __restrict__ dst, const float* __restrict__ g
 template <typename WT>
 __global__ void k_route(float* __restrict__ dst, const float* __restrict__ logits, const WT* __restrict__ corr, uint32_t T, uint32_t NE, uint32_t top,
                         uint32_t logits_rs) {
+    pdl_enter();
     extern __shared__ float sm[];                      // [warps][NE] choice scores
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t t = blockIdx.x * (blockDim.x >> 5) + warp;
@@ -528,12 +652,15 @@ template <typename WT>
 __device__ __forceinline__ float warp_dot(const WT* __restrict__ w, const float* __restrict__ x, uint32_t K, uint32_t lane) {
     constexpr int V = WVec<WT>::n;
     float acc = 0.0f;
-    if (K % V == 0 && (reinterpret_cast<size_t>(w) & 15) == 0) {
+    if (K % V == 0 && (reinterpret_cast<size_t>(w) & 15) == 0 && (reinterpret_cast<size_t>(x) & 15) == 0) {
         for (uint32_t k = lane * V; k < K; k += 32 * V) {
             float wv[V];
             wld_vec<WT>(w + k, wv);
 #pragma unroll
-            for (int i = 0; i < V; i++) acc = fmaf(x[k + i], wv[i], acc);
+            for (int i = 0; i < V / 4; i++) {
+                const float4 xv = *reinterpret_cast<const float4*>(x + k + 4 * i);
+                acc = fmaf(xv.x, wv[4 * i], fmaf(xv.y, wv[4 * i + 1], fmaf(xv.z, wv[4 * i + 2], fmaf(xv.w, wv[4 * i + 3], acc))));
+            }
         }
     } else {
         for (uint32_t k = lane; k < K; k += 32) acc = fmaf(x[k], wld(w, k), acc);
@@ -544,12 +671,20 @@ __device__ __forceinline__ float warp_dot(const WT* __restrict__ w, const float*
 // ── MOE_FFN, token-wise form: every (token, choice) pair streams the rows of its expert (decode and short steps) ────────
 template <typename WT>
 __global__ void k_moe_up(float* __restrict__ y, const float* __restrict__ src, const float* __restrict__ route, const WT* __restrict__ wg,
-                         const WT* __restrict__ wu, uint32_t D, uint32_t ff, uint32_t E, uint32_t top, float limit, float alpha) {
+                         const WT* __restrict__ wu, uint32_t D, uint32_t ff, uint32_t E, uint32_t top, float limit, float alpha, uint32_t stage) {
+    pdl_enter();
     const uint32_t pair = blockIdx.y;                  // token * top + choice
     const uint32_t f = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     const uint32_t e = (uint32_t)reinterpret_cast<const int*>(route)[2 * (size_t)pair];
-    if (f >= ff || e >= E) return;                     // identity experts have no weights
+    if (e >= E) return;                                // identity experts have no weights (uniform over the CTA)
+    extern __shared__ __align__(16) float xsh[];       // the token's input, staged once per CTA when it fits
     const float* x = src + (size_t)(pair / top) * D;
+    if (stage) {
+        for (uint32_t c = threadIdx.x; c < D; c += blockDim.x) xsh[c] = x[c];
+        __syncthreads();
+        x = xsh;
+    }
+    if (f >= ff) return;
     const size_t row = ((size_t)e * ff + f) * D;
     float g = warp_dot(wg + row, x, D, lane), u = warp_dot(wu + row, x, D, lane);
     g = fminf(g, limit);
@@ -559,6 +694,7 @@ __global__ void k_moe_up(float* __restrict__ y, const float* __restrict__ src, c
 template <typename WT>
 __global__ void k_moe_down(float* __restrict__ dst, const float* __restrict__ src, const float* __restrict__ y, const float* __restrict__ route,
                            const WT* __restrict__ wd, uint32_t D, uint32_t ff, uint32_t E, uint32_t top) {
+    pdl_enter();
     const uint32_t t = blockIdx.y;
     const uint32_t d = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (d >= D) return;
@@ -807,7 +943,19 @@ uint32_t zg_seq_op_writes(uint32_t tag) {
 
 // f32 slots of the shared activation scratch this op needs (0: none): a LINEAR over bfloat16 weights with more rows than the
 // row kernels take runs on the tensor cores (dense_gemm.cu) from a bf16 copy of its input.  ZG_DENSE_GEMM=0 keeps the exact tile.
+// window shares per (token, head) of a WINDOW_ATTENTION step: few pairs and a long window (decode) spread over more CTAs
+static uint32_t attention_splits(const ZgSeqOp& s) {
+    const uint32_t pairs = s.n[0] * s.n[1], window = s.n[5];
+    if (s.n[3] % 4 || pairs >= 128 || window < 128) return 1;
+    uint32_t S = (256 + pairs - 1) / pairs;
+    if (S > window / 32) S = window / 32;
+    return S < 2 ? 1 : (S > 16 ? 16 : S);
+}
 size_t zg_seq_op_scratch_elems(const ZgOp& op, float* const* bufs) {
+    if (op.tag == ZG_OP_WINDOW_ATTENTION) {
+        const uint32_t S = attention_splits(op.u.seq);
+        return S > 1 ? (size_t)op.u.seq.n[0] * op.u.seq.n[1] * S * (4 + op.u.seq.n[3]) : 0;
+    }
     if (!dense_gemm_enabled() || op.tag != ZG_OP_LINEAR || op.u.seq.n[5] != ZG_W_BF16) return 0;
     const ZgSeqOp& s = op.u.seq;
     if (!zg_dense_gemm_usable(wptr<bf16>(bufs, s.buf[2], s.off[0]), s.n[0], s.n[1], s.n[2])) return 0;
@@ -819,7 +967,7 @@ bool zg_launch_seq_op(ZgCudaCtx* ctx, const ZgOp& op, float* const* bufs, float*
     const ZgSeqOp& s = op.u.seq;
     switch (op.tag) {
         case ZG_OP_EMBED:
-            ZG_SEQ_WDT(s.n[2], k_embed<WT><<<s.n[0], 128, 0, st>>>(bufs[s.buf[0]], bufs[s.buf[1]], wptr<WT>(bufs, s.buf[2], s.off[0]), s.n[1], s.f[0]));
+            ZG_SEQ_WDT(s.n[2], launch_pdl(k_embed<WT>, dim3(s.n[0]), dim3(128), 0, st, bufs[s.buf[0]], bufs[s.buf[1]], wptr<WT>(bufs, s.buf[2], s.off[0]), s.n[1], s.f[0]));
             ZG_SEQ_CHECK();
             return true;
         case ZG_OP_LINEAR: {
@@ -835,12 +983,13 @@ bool zg_launch_seq_op(ZgCudaCtx* ctx, const ZgOp& op, float* const* bufs, float*
                 const WT* b = has_bias ? wptr<WT>(bufs, s.buf[3], s.off[1]) : nullptr;
                 constexpr uint32_t V = WVec<WT>::n;
                 if (M <= kGemvRows) {
-                    const bool vec = K % V == 0 && (reinterpret_cast<size_t>(W) & 15) == 0 && (reinterpret_cast<size_t>(src) & 15) == 0 && s.n[3] % 4 == 0;
+                    const size_t xs_bytes = (size_t)M * K * sizeof(float);
+                    const bool vec = K % V == 0 && (reinterpret_cast<size_t>(W) & 15) == 0 && xs_bytes <= 48 * 1024;
                     const dim3 grid((N + 7) / 8);
-                    if (vec && M == 1) k_linear_rows_vec<WT, 1><<<grid, 256, 0, st>>>(dst, src, W, b, M, N, K, s.n[3], s.n[4]);
-                    else if (vec && M <= 4) k_linear_rows_vec<WT, 4><<<grid, 256, 0, st>>>(dst, src, W, b, M, N, K, s.n[3], s.n[4]);
-                    else if (vec) k_linear_rows_vec<WT, 8><<<grid, 256, 0, st>>>(dst, src, W, b, M, N, K, s.n[3], s.n[4]);
-                    else k_linear_rows<WT><<<grid, 256, 0, st>>>(dst, src, W, b, M, N, K, s.n[3], s.n[4]);
+                    if (vec && M == 1) launch_pdl(k_linear_rows_vec<WT, 1>, dim3(grid), dim3(256), xs_bytes, st, dst, src, W, b, M, N, K, s.n[3], s.n[4]);
+                    else if (vec && M <= 4) launch_pdl(k_linear_rows_vec<WT, 4>, dim3(grid), dim3(256), xs_bytes, st, dst, src, W, b, M, N, K, s.n[3], s.n[4]);
+                    else if (vec) launch_pdl(k_linear_rows_vec<WT, 8>, dim3(grid), dim3(256), xs_bytes, st, dst, src, W, b, M, N, K, s.n[3], s.n[4]);
+                    else launch_pdl(k_linear_rows<WT>, dim3(grid), dim3(256), 0, st, dst, src, W, b, M, N, K, s.n[3], s.n[4]);
                 } else {
                     const dim3 grid((N + kTN - 1) / kTN, (M + kTM - 1) / kTM);
                     k_linear_tile<WT><<<grid, 256, 0, st>>>(dst, src, W, b, M, N, K, s.n[3], s.n[4]);
@@ -851,13 +1000,13 @@ bool zg_launch_seq_op(ZgCudaCtx* ctx, const ZgOp& op, float* const* bufs, float*
         }
         case ZG_OP_NORM: {
             const float* res = s.buf[3] != ZG_NO_BUF ? bufs[s.buf[3]] : nullptr;
-            ZG_SEQ_WDT(s.n[3], k_norm<WT><<<s.n[0], 256, 0, st>>>(bufs[s.buf[0]], bufs[s.buf[1]], wptr<WT>(bufs, s.buf[2], s.off[0]), res, s.n[1], s.n[2], s.f[0]));
+            ZG_SEQ_WDT(s.n[3], launch_pdl(k_norm<WT>, dim3(s.n[0]), dim3(256), 0, st, bufs[s.buf[0]], bufs[s.buf[1]], wptr<WT>(bufs, s.buf[2], s.off[0]), res, s.n[1], s.n[2], s.f[0]));
             ZG_SEQ_CHECK();
             return true;
         }
         case ZG_OP_WINDOW_ATTENTION: {
             const uint32_t T = s.n[0], H = s.n[1], G = s.n[2], dim = s.n[3];
-            k_ring_append<<<T, 128, 0, st>>>(bufs[s.buf[2]], bufs[s.buf[1]], bufs[s.buf[4]], s.off[1], s.n[4], G * dim, s.n[6]);
+            launch_pdl(k_ring_append, dim3(T), dim3(128), 0, st, bufs[s.buf[2]], bufs[s.buf[1]], bufs[s.buf[4]], s.off[1], s.n[4], G * dim, s.n[6]);
             ZG_SEQ_CHECK();
             const size_t width = (size_t)G * dim;
             const bool vec = dim % 4 == 0 && s.off[0] % 4 == 0 && s.n[4] % 4 == 0 && width % 4 == 0 && (reinterpret_cast<uintptr_t>(bufs[s.buf[1]]) & 15) == 0 &&
@@ -866,17 +1015,23 @@ bool zg_launch_seq_op(ZgCudaCtx* ctx, const ZgOp& op, float* const* bufs, float*
                 const uint32_t CH = dim > 128 ? 2 : 1;
                 uint32_t LK = 1;
                 while (LK * 4 * CH < dim) LK <<= 1;
-                const uint32_t nw = T * H <= 64 ? 16 : (T * H <= 1024 ? 8 : 4);
+                const uint32_t S = scratch ? attention_splits(s) : 1;
+                float* part = S > 1 ? scratch : nullptr;
+                const uint32_t nw = S > 1 ? 4 : (T * H <= 64 ? 16 : (T * H <= 1024 ? 8 : 4));
                 const size_t smem = (size_t)nw * (4 + dim) * sizeof(float);
                 if (CH == 1)
-                    k_window_attention_v<1><<<T * H, nw * 32, smem, st>>>(bufs[s.buf[0]], bufs[s.buf[1]], bufs[s.buf[2]], bufs[s.buf[3]], bufs[s.buf[4]], H, G, dim, LK,
-                                                                        s.n[4], s.off[0], s.off[2], s.n[5], s.n[6], s.f[0], s.f[1]);
+                    launch_pdl(k_window_attention_v<1>, dim3(T * H, S), dim3(nw * 32), smem, st, bufs[s.buf[0]], bufs[s.buf[1]], bufs[s.buf[2]], bufs[s.buf[3]], bufs[s.buf[4]], H, G, dim, LK,
+                                                                        s.n[4], s.off[0], s.off[2], s.n[5], s.n[6], s.f[0], s.f[1], part);
                 else
-                    k_window_attention_v<2><<<T * H, nw * 32, smem, st>>>(bufs[s.buf[0]], bufs[s.buf[1]], bufs[s.buf[2]], bufs[s.buf[3]], bufs[s.buf[4]], H, G, dim, LK,
-                                                                        s.n[4], s.off[0], s.off[2], s.n[5], s.n[6], s.f[0], s.f[1]);
+                    launch_pdl(k_window_attention_v<2>, dim3(T * H, S), dim3(nw * 32), smem, st, bufs[s.buf[0]], bufs[s.buf[1]], bufs[s.buf[2]], bufs[s.buf[3]], bufs[s.buf[4]], H, G, dim, LK,
+                                                                        s.n[4], s.off[0], s.off[2], s.n[5], s.n[6], s.f[0], s.f[1], part);
+                if (S > 1) {
+                    ZG_SEQ_CHECK();
+                    launch_pdl(k_window_attention_merge, dim3(T * H), dim3(128), 0, st, bufs[s.buf[0]], bufs[s.buf[1]], part, H, dim, S, s.n[4], s.off[2]);
+                }
             } else {
                 const uint32_t warps = 4;
-                k_window_attention<<<(T * H + warps - 1) / warps, warps * 32, warps * dim * sizeof(float), st>>>(
+                launch_pdl(k_window_attention, dim3((T * H + warps - 1) / warps), dim3(warps * 32), warps * dim * sizeof(float), st, 
                     bufs[s.buf[0]], bufs[s.buf[1]], bufs[s.buf[2]], bufs[s.buf[3]], bufs[s.buf[4]], T, H, G, dim, s.n[4], s.off[0], s.off[2], s.n[5], s.n[6], s.f[0], s.f[1]);
             }
             ZG_SEQ_CHECK();
@@ -887,11 +1042,11 @@ bool zg_launch_seq_op(ZgCudaCtx* ctx, const ZgOp& op, float* const* bufs, float*
             float* dst = bufs[s.buf[0]] + s.off[2];
             const float* src = bufs[s.buf[1]] + s.off[1];
             const size_t n = (size_t)T * C;
-            ZG_SEQ_WDT(s.n[6], k_causal_conv<WT><<<(unsigned)((n + 255) / 256), 256, 0, st>>>(dst, src, wptr<WT>(bufs, s.buf[2], s.off[0]), bufs[s.buf[3]], bufs[s.buf[4]],
+            ZG_SEQ_WDT(s.n[6], launch_pdl(k_causal_conv<WT>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, dst, src, wptr<WT>(bufs, s.buf[2], s.off[0]), bufs[s.buf[3]], bufs[s.buf[4]],
                                                                                           T, C, taps, s.n[3], s.n[4], s.n[5]));
             ZG_SEQ_CHECK();
             if (taps > 1) {
-                k_conv_advance<<<(C + 127) / 128, 128, 0, st>>>(bufs[s.buf[3]], src, bufs[s.buf[4]], T, C, taps, s.n[3]);
+                launch_pdl(k_conv_advance, dim3((C + 127) / 128), dim3(128), 0, st, bufs[s.buf[3]], src, bufs[s.buf[4]], T, C, taps, s.n[3]);
                 ZG_SEQ_CHECK();
             }
             return true;
@@ -903,18 +1058,18 @@ bool zg_launch_seq_op(ZgCudaCtx* ctx, const ZgOp& op, float* const* bufs, float*
             const dim3 grid((vdim + cols - 1) / cols, H);
             ZG_SEQ_WDT(s.n[9], {
                 if (smem > 48 * 1024) cudaFuncSetAttribute(k_delta_rule<WT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-                k_delta_rule<WT><<<grid, kDeltaThreads, smem, st>>>(bufs[s.buf[0]], bufs[s.buf[1]], bufs[s.buf[2]], bufs[s.buf[3]], wptr<WT>(bufs, s.buf[5], 0), bufs[s.buf[6]],
+                launch_pdl(k_delta_rule<WT>, dim3(grid), dim3(kDeltaThreads), smem, st, bufs[s.buf[0]], bufs[s.buf[1]], bufs[s.buf[2]], bufs[s.buf[3]], wptr<WT>(bufs, s.buf[5], 0), bufs[s.buf[6]],
                                                                   bufs[s.buf[7]], T, H, G, dim, vdim, RS, s.off[0], s.off[1], s.off[2], s.off[3], s.off[4], s.off[5],
                                                                   s.n[5], s.n[6], s.n[7], s.f[1], s.f[2]);
             });
             ZG_SEQ_CHECK();
-            ZG_SEQ_WDT(s.n[9], k_delta_out<WT><<<(T * H + 3) / 4, 128, 0, st>>>(bufs[s.buf[0]], bufs[s.buf[4]], wptr<WT>(bufs, s.buf[5], 0), T * H, H, vdim, s.n[8], s.off[6], s.f[0]));
+            ZG_SEQ_WDT(s.n[9], launch_pdl(k_delta_out<WT>, dim3((T * H + 3) / 4), dim3(128), 0, st, bufs[s.buf[0]], bufs[s.buf[4]], wptr<WT>(bufs, s.buf[5], 0), T * H, H, vdim, s.n[8], s.off[6], s.f[0]));
             ZG_SEQ_CHECK();
             return true;
         }
         case ZG_OP_ROUTE: {
             const uint32_t T = s.n[0], NE = s.n[1];
-            ZG_SEQ_WDT(s.n[4], k_route<WT><<<(T + 3) / 4, 128, 4 * NE * sizeof(float), st>>>(bufs[s.buf[0]], bufs[s.buf[1]] + s.off[1], wptr<WT>(bufs, s.buf[2], s.off[0]), T, NE,
+            ZG_SEQ_WDT(s.n[4], launch_pdl(k_route<WT>, dim3((T + 3) / 4), dim3(128), 4 * NE * sizeof(float), st, bufs[s.buf[0]], bufs[s.buf[1]] + s.off[1], wptr<WT>(bufs, s.buf[2], s.off[0]), T, NE,
                                                                                          s.n[2], s.n[3]));
             ZG_SEQ_CHECK();
             return true;
@@ -942,11 +1097,12 @@ bool zg_launch_seq_op(ZgCudaCtx* ctx, const ZgOp& op, float* const* bufs, float*
             }
             ZG_SEQ_WDT(s.n[5], {
                 if (E && ff) {
-                    k_moe_up<WT><<<dim3((ff + 7) / 8, T * top), 256, 0, st>>>(bufs[s.buf[4]], bufs[s.buf[1]], bufs[s.buf[2]], wptr<WT>(bufs, s.buf[3], s.off[0]),
-                                                                           wptr<WT>(bufs, s.buf[3], s.off[1]), D, ff, E, top, s.f[0], s.f[1]);
+                    const uint32_t stage = (size_t)D * 4 <= 48 * 1024 ? 1u : 0u;
+                    launch_pdl(k_moe_up<WT>, dim3(dim3((ff + 7) / 8, T * top)), dim3(256), stage ? D * sizeof(float) : 0, st, bufs[s.buf[4]], bufs[s.buf[1]], bufs[s.buf[2]], wptr<WT>(bufs, s.buf[3], s.off[0]),
+                                                                           wptr<WT>(bufs, s.buf[3], s.off[1]), D, ff, E, top, s.f[0], s.f[1], stage);
                     ZG_COUNT_LAUNCH();
                 }
-                k_moe_down<WT><<<dim3((D + 7) / 8, T), 256, 0, st>>>(bufs[s.buf[0]], bufs[s.buf[1]], bufs[s.buf[4]], bufs[s.buf[2]], wptr<WT>(bufs, s.buf[3], s.off[2]), D, ff, E, top);
+                launch_pdl(k_moe_down<WT>, dim3(dim3((D + 7) / 8, T)), dim3(256), 0, st, bufs[s.buf[0]], bufs[s.buf[1]], bufs[s.buf[4]], bufs[s.buf[2]], wptr<WT>(bufs, s.buf[3], s.off[2]), D, ff, E, top);
             });
             ZG_SEQ_CHECK();
             return true;
