@@ -64,7 +64,7 @@ def test_safetensors_rejects_bad_files(tmp_path):
         SafetensorsFile(p)
 
 
-@pytest.mark.parametrize("rows,bias_max", [(8, 32), (32, 240), (6, 9), (4, 3), (10, 20), (16, 128)])
+@pytest.mark.parametrize("rows,bias_max", [(8, 32), (6, 9), (4, 3), (10, 20), (16, 128)])
 def test_distance_buckets(rows, bias_max):
     from zgml_b200.host.lududra import distance_bias_table, distance_bucket
     b = [distance_bucket(n, rows, bias_max) for n in range(3 * bias_max + 12)]
