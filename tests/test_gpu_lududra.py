@@ -276,3 +276,45 @@ def test_long_window_decode_splits_the_window(cuda_backend):
     got = [s.feed("r", toks[:130], range(130))] + [s.feed("r", [t], [0]) for t in toks[130:]]
     assert rel(np.concatenate(got), want) < TOL
     close(s)
+
+
+# ── the prefill kernels: tiles of queries, keys and tokens ──
+@pytest.mark.parametrize("window,dim,first", [(63, 16, 0), (64, 48, 37), (65, 20, 1), (100, 128, 64), (129, 8, 5), (3, 36, 70), (300, 16, 11)])
+def test_tiled_prefill_attention_at_tile_borders(cuda_backend, window, dim, first):
+    """Chunks of up to 128 tokens take the tiled prefill kernel: windows that end just before, at and just after a 64-key
+    tile, head sizes that pad the tile, chunks that start anywhere in the sequence, a peaky softmax (one key more or less
+    is far outside the tolerance), against the restatement and against single-token steps."""
+    cfg = config([attention_layer(heads=4, kv_heads=2, dim=dim, window=window, rel_rows=10, bias_max=2 * window + 3, softcap=25.0)], width=32, vocab=50)
+    W = random_weights(cfg, seed=window, qk_gain=10.0)
+    n = first + 128 + 64 + 16 + 3
+    toks = tokens(cfg, n)
+    want, _ = ref.forward(cfg, as_f64(W), toks)
+    if window < n:
+        wider = json.loads(json.dumps(cfg))
+        wider["layers"][0]["mixer"]["mask"]["size"] = window + 1
+        assert rel(ref.forward(wider, as_f64(W), toks)[0], want) > 50 * TOL
+    s = open_model(cuda_backend, cfg, W, n_slots=2, max_chunk=128)
+    got = ([s.feed("p", toks[:first], range(first))] if first else []) + [s.feed("p", toks[first:], range(n - first))]
+    assert rel(np.concatenate(got), want) < TOL
+    single = np.concatenate([s.feed("d", [t], [0]) for t in toks])
+    assert rel(single, want) < TOL
+    close(s)
+
+
+@pytest.mark.parametrize("layer", [delta_layer(), delta_layer(heads=3, kv_heads=1, dim=40, vdim=10, conv=4, rank_a=3, rank_g=5),
+                                   delta_layer(heads=2, kv_heads=2, dim=8, vdim=70, conv=1), delta_layer(heads=1, kv_heads=1, dim=130, vdim=12, conv=2),
+                                   delta_layer(heads=4, kv_heads=2, dim=128, vdim=32, conv=3)],
+                         ids=["delta", "delta-odd", "delta-notail", "delta-wide-key", "delta-128"])
+def test_delta_prefill_walks_prepared_tiles(cuda_backend, layer):
+    """Chunks of 16 or more tokens prepare every token's vectors first and walk them tile by tile (double buffered): several
+    tiles, chunks of both kinds in one sequence, against the restatement and single tokens."""
+    cfg = config([layer], width=40, vocab=61)
+    W = random_weights(cfg, seed=17)
+    toks = tokens(cfg, 64 + 16 + 8 + 2 + 1 + 64 + 32)
+    want, _ = ref.forward(cfg, as_f64(W), toks)
+    s = open_model(cuda_backend, cfg, W, n_slots=2, max_chunk=64)
+    got = [s.feed("p", toks[:91], range(91)), s.feed("p", toks[91:], range(96))]
+    assert rel(np.concatenate(got), want) < 2 * TOL
+    single = np.concatenate([s.feed("d", [t], [0]) for t in toks])
+    assert rel(single, want) < 2 * TOL
+    close(s)

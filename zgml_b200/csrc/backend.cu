@@ -2114,7 +2114,7 @@ extern "C" uint64_t zg_cuda_program_stats(const ZgCudaProgram* p, int what) {
     if (!p) return 0;
     switch (what) {
         case 5: return zg_dense_gemm_timeouts();
-        case 6: { uint64_t n = 0; for (const ZgOp& op : p->ops) if (zg_is_seq_op(op.tag) && zg_seq_op_scratch_elems(op, p->buffers.data())) n++; return n; }
+        case 6: { uint64_t n = 0; for (const ZgOp& op : p->ops) if (op.tag == ZG_OP_LINEAR && zg_seq_op_scratch_elems(op, p->buffers.data())) n++; return n; }
         case 0: return p->graph_kernels;
         case 1: return p->dec.valid ? p->dec_count : 0;
         case 2: return p->dec.valid ? p->dec.plan.n_layers : 0;

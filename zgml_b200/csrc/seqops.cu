@@ -478,6 +478,156 @@ __global__ void k_window_attention_merge(float* __restrict__ dst, const float* _
     }
 }
 
+// Prefill form of WINDOW_ATTENTION (16 or more tokens, head size up to 128): flash tiling in f32, as the framework's causal
+// prefill attention does.  One CTA owns 64 consecutive queries of one head and walks the keys its window reaches in tiles
+// of 64 ring rows.  The key tile in shared memory serves the scores AND, keys being the values, the weighted sum.  Thread
+// (ty, tx) of 16 x 16 holds queries 4 ty .. 4 ty + 3 against keys tx + 16 c (conflict-free float4 reads of padded key rows);
+// the row statistics of the running softmax are shared by the 16 threads of a row through half-warp shuffles; the
+// probabilities pass through shared memory; outputs tx + 16 c of the four rows accumulate in registers.  The distance
+// biases a tile can meet (127 distances) are staged once per tile, -inf standing for "outside the window or the future".
+// The sink joins the denominator at the end, then the output gate.  DH = 16 OC covers the head; channels past dim are zero.
+constexpr int kWaBQ = 64, kWaBK = 64, kWaThreads = 256, kWaTiledMinTokens = 16;
+template <int OC>
+__global__ void __launch_bounds__(kWaThreads, 2)
+k_window_attention_tiled(float* __restrict__ dst, const float* __restrict__ proj, const float* __restrict__ ring, const float* __restrict__ bias,
+                         const float* __restrict__ ctl, uint32_t T, uint32_t H, uint32_t G, uint32_t dim, uint32_t proj_rs, uint32_t q_off,
+                         uint32_t g_off, uint32_t window, uint32_t R, float scale, float cap) {
+    pdl_enter();
+    constexpr int DH = 16 * OC, KP = DH + 4, PP = kWaBK + 4;
+    extern __shared__ __align__(16) float sm[];
+    float* Qs = sm;                                    // [64][DH]
+    float* Ks = Qs + kWaBQ * DH;                       // [64][DH + 4]
+    float* Ps = Ks + kWaBK * KP;                       // [64][64 + 4]
+    float* Bs = Ps + kWaBQ * PP;                       // [128]
+    const uint32_t h = blockIdx.y, kv = h / (H / G), t0 = blockIdx.x * kWaBQ;
+    const uint32_t tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    const uint32_t pos0 = (uint32_t)ctl_word(ctl, ZG_CTL_POS), slot = (uint32_t)ctl_word(ctl, ZG_CTL_SLOT);
+    const uint32_t nq = min((uint32_t)kWaBQ, T - t0);
+    const uint32_t p_first = pos0 + t0, p_last = p_first + nq - 1;
+    const uint32_t lo = p_first + 1 >= window ? p_first + 1 - window : 0;
+    const size_t width = (size_t)G * dim;
+    const float* base = ring + (size_t)slot * R * width + (size_t)kv * dim;
+    for (uint32_t i = tid; i < kWaBQ * (DH / 4); i += kWaThreads) {
+        const uint32_t r = i / (DH / 4), c4 = i % (DH / 4);
+        float4 val = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (r < nq && 4 * c4 < dim) val = *reinterpret_cast<const float4*>(proj + (size_t)(t0 + r) * proj_rs + q_off + (size_t)h * dim + 4 * c4);
+        *reinterpret_cast<float4*>(Qs + r * DH + 4 * c4) = val;
+    }
+    float o[4][OC], m_run[4], l_run[4];
+#pragma unroll
+    for (int r = 0; r < 4; r++) {
+        m_run[r] = -INFINITY; l_run[r] = 0.0f;
+#pragma unroll
+        for (int c = 0; c < OC; c++) o[r][c] = 0.0f;
+    }
+    for (uint32_t s0 = lo; s0 <= p_last; s0 += kWaBK) {
+        __syncthreads();                               // the previous tile's readers of Ks / Ps / Bs are done
+        for (uint32_t i = tid; i < kWaBK * (DH / 4); i += kWaThreads) {
+            const uint32_t r = i / (DH / 4), c4 = i % (DH / 4);
+            float4 val = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (s0 + r <= p_last && 4 * c4 < dim) val = *reinterpret_cast<const float4*>(base + (size_t)((s0 + r) % R) * width + 4 * c4);
+            *reinterpret_cast<float4*>(Ks + r * KP + 4 * c4) = val;
+        }
+        if (tid < 2 * kWaBK - 1) {                     // distance of (query row a, key column b) = p_first - s0 + a - b
+            const int d = (int)p_first - (int)s0 - (kWaBK - 1) + (int)tid;
+            Bs[tid] = (d >= 0 && d < (int)window) ? bias[(size_t)d * H + h] : -INFINITY;
+        }
+        __syncthreads();
+        float sc[4][4];
+#pragma unroll
+        for (int r = 0; r < 4; r++)
+#pragma unroll
+            for (int c = 0; c < 4; c++) sc[r][c] = 0.0f;
+#pragma unroll 2
+        for (int d = 0; d < DH; d += 4) {
+            float4 qa[4], ka[4];
+#pragma unroll
+            for (int r = 0; r < 4; r++) qa[r] = *reinterpret_cast<const float4*>(Qs + (4 * ty + r) * DH + d);
+#pragma unroll
+            for (int c = 0; c < 4; c++) ka[c] = *reinterpret_cast<const float4*>(Ks + (tx + 16 * c) * KP + d);
+#pragma unroll
+            for (int r = 0; r < 4; r++)
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    sc[r][c] = fmaf(qa[r].x, ka[c].x, sc[r][c]); sc[r][c] = fmaf(qa[r].y, ka[c].y, sc[r][c]);
+                    sc[r][c] = fmaf(qa[r].z, ka[c].z, sc[r][c]); sc[r][c] = fmaf(qa[r].w, ka[c].w, sc[r][c]);
+                }
+        }
+#pragma unroll
+        for (int r = 0; r < 4; r++) {
+            const uint32_t a = 4 * ty + r;
+            float rmax = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                const float b = Bs[a + (kWaBK - 1) - (tx + 16 * c)];
+                float sv = -INFINITY;
+                if (a < nq && b != -INFINITY) {
+                    sv = sc[r][c] * scale;
+                    if (cap > 0.0f) sv = cap * tanhf(sv / cap);
+                    sv += b;
+                }
+                sc[r][c] = sv;
+                rmax = fmaxf(rmax, sv);
+            }
+#pragma unroll
+            for (int off = 8; off > 0; off >>= 1) rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, off));
+            const float new_m = fmaxf(m_run[r], rmax);
+            const float alpha = m_run[r] == -INFINITY ? (new_m == -INFINITY ? 1.0f : 0.0f) : expf(m_run[r] - new_m);
+            float rsum = 0.0f;
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                const float pv = sc[r][c] == -INFINITY ? 0.0f : expf(sc[r][c] - new_m);
+                Ps[a * PP + tx + 16 * c] = pv;
+                rsum += pv;
+            }
+#pragma unroll
+            for (int off = 8; off > 0; off >>= 1) rsum += __shfl_xor_sync(0xffffffffu, rsum, off);
+            l_run[r] = l_run[r] * alpha + rsum;
+            m_run[r] = new_m;
+#pragma unroll
+            for (int c = 0; c < OC; c++) o[r][c] *= alpha;
+        }
+        __syncthreads();
+#pragma unroll 4
+        for (int j = 0; j < kWaBK; j++) {
+            float pj[4], vj[OC];
+#pragma unroll
+            for (int r = 0; r < 4; r++) pj[r] = Ps[(4 * ty + r) * PP + j];
+#pragma unroll
+            for (int c = 0; c < OC; c++) vj[c] = Ks[j * KP + tx + 16 * c];
+#pragma unroll
+            for (int r = 0; r < 4; r++)
+#pragma unroll
+                for (int c = 0; c < OC; c++) o[r][c] = fmaf(pj[r], vj[c], o[r][c]);
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < 4; r++) {
+        const uint32_t a = 4 * ty + r;
+        if (a >= nq) continue;
+        // every query sees itself, so m_run is finite; the sink (score 0, no value) joins the denominator here
+        const float Ms = fmaxf(m_run[r], 0.0f);
+        const float wk = expf(m_run[r] - Ms);
+        const float inv = wk / (expf(-Ms) + l_run[r] * wk);
+        const float* grow = proj + (size_t)(t0 + a) * proj_rs + g_off + (size_t)h * dim;
+        float* out = dst + ((size_t)(t0 + a) * H + h) * dim;
+#pragma unroll
+        for (int c = 0; c < OC; c++) {
+            const uint32_t col = tx + 16 * c;
+            if (col < dim) out[col] = o[r][c] * inv * sigmoidf_(grow[col]);
+        }
+    }
+}
+template <int OC>
+static void launch_window_attention_tiled(const ZgSeqOp& s, float* const* bufs, cudaStream_t st) {
+    constexpr int DH = 16 * OC;
+    const size_t smem = ((size_t)kWaBQ * DH + (size_t)kWaBK * (DH + 4) + (size_t)kWaBQ * (kWaBK + 4) + 2 * kWaBK) * sizeof(float);
+    static bool once = false;
+    if (!once) { cudaFuncSetAttribute(k_window_attention_tiled<OC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); once = true; }
+    launch_pdl(k_window_attention_tiled<OC>, dim3((s.n[0] + kWaBQ - 1) / kWaBQ, s.n[1]), dim3(kWaThreads), smem, st, bufs[s.buf[0]], bufs[s.buf[1]], bufs[s.buf[2]],
+               bufs[s.buf[3]], bufs[s.buf[4]], s.n[0], s.n[1], s.n[2], s.n[3], s.n[4], s.off[0], s.off[2], s.n[5], s.n[6], s.f[0], s.f[1]);
+}
+
 // ── CAUSAL_CONV ──────────────────────────────────────────────────────────────────────────────────────────────────
 template <typename WT>
 __global__ void k_causal_conv(float* __restrict__ dst, const float* __restrict__ src, const WT* __restrict__ w, const float* __restrict__ state,
@@ -591,6 +741,126 @@ __global__ void __launch_bounds__(kDeltaThreads) k_delta_rule(
 #pragma unroll
     for (int i = 0; i < kDeltaRows; i++) {
         const uint32_t row = r * kDeltaRows + i;
+        if (live && row < dim) S_g[(size_t)row * vdim + col] = S[i];
+    }
+}
+// Prefill form of DELTA_RULE (kDeltaPrepMinTokens or more tokens): the per-token vectors are prepared for ALL tokens at
+// once by k_delta_prepare (one warp per (token, head); the walk's critical path then holds no transcendental and no global
+// read), into rows [unit k | scaled unit q | decay | beta, k . q, 0, 0] of 3 dpad + 4 floats laid out [head][token], so
+// that a tile of tokens is one contiguous, 16-byte aligned block.  k_delta_walk streams those tiles into shared memory with
+// cp.async, double buffered, and walks the tokens.  Per token a thread scales its rows by the decay and takes BOTH dot
+// products, with k and with q, in the same pass; one shuffle round reduces them together.  The read-out after the write
+// follows from  o = (g S)^T q + u (k . q), so the state update S <- g S + k u^T leaves the output's critical path.
+// A thread's kDeltaRows rows are four groups of four consecutive rows, group c of slice r at row (c RS + r) 4: the RS slices
+// of a column read consecutive float4s of a prepared vector (no bank conflict; the columns of a warp read the same words).
+constexpr int kDeltaPrepMinTokens = 16;
+__device__ __forceinline__ uint32_t delta_row(uint32_t RS, uint32_t r, int i) { return (((uint32_t)i >> 2) * RS + r) * 4 + ((uint32_t)i & 3); }
+template <typename WT>
+__global__ void k_delta_prepare(float* __restrict__ prep, const float* __restrict__ qkv, const float* __restrict__ betab, const float* __restrict__ ab,
+                                const WT* __restrict__ wts, uint32_t T, uint32_t H, uint32_t G, uint32_t dim, uint32_t dpad, uint32_t q_off,
+                                uint32_t k_off, uint32_t beta_off, uint32_t A_off, uint32_t dt_off, uint32_t qkv_rs, uint32_t beta_rs, uint32_t a_rs,
+                                float unit_eps, float q_scale) {
+    pdl_enter();
+    const uint32_t w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (w >= T * H) return;
+    const uint32_t t = w / H, h = w % H, kv = h / (H / G);
+    const float* qr = qkv + (size_t)t * qkv_rs + q_off + (size_t)kv * dim;
+    const float* kr = qkv + (size_t)t * qkv_rs + k_off + (size_t)kv * dim;
+    const float* ar = ab + (size_t)t * a_rs + (size_t)h * dim;
+    float qq = 0.0f, kk = 0.0f, qk = 0.0f;
+    for (uint32_t c = lane; c < dim; c += 32) { const float a = qr[c], b = kr[c]; qq = fmaf(a, a, qq); kk = fmaf(b, b, kk); qk = fmaf(a, b, qk); }
+    const float qn = q_scale / sqrtf(warp_sum(qq) + unit_eps), kn = 1.0f / sqrtf(warp_sum(kk) + unit_eps);
+    qk = warp_sum(qk) * qn * kn;
+    const float Ah = expf(wld(wts, (size_t)A_off + h));
+    float* row = prep + ((size_t)h * T + t) * (3 * dpad + 4);
+    for (uint32_t c = lane; c < dpad; c += 32) {
+        const bool in = c < dim;
+        row[c] = in ? kr[c] * kn : 0.0f;
+        row[dpad + c] = in ? qr[c] * qn : 0.0f;
+        row[2 * dpad + c] = in ? expf(-Ah * softplusf_(ar[c] + wld(wts, (size_t)dt_off + (size_t)h * dim + c))) : 1.0f;
+    }
+    if (lane < 4) row[3 * dpad + lane] = lane == 0 ? sigmoidf_(betab[(size_t)t * beta_rs + beta_off + h]) : (lane == 1 ? qk : 0.0f);
+}
+__device__ __forceinline__ void cp_async16(float* smem_dst, const float* gmem_src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gmem_src) : "memory");
+}
+__global__ void __launch_bounds__(kDeltaThreads) k_delta_walk(float* __restrict__ dst, const float* __restrict__ qkv, const float* __restrict__ prep,
+                                                               float* __restrict__ state, const float* __restrict__ ctl, uint32_t T, uint32_t H,
+                                                               uint32_t dim, uint32_t vdim, uint32_t RS, uint32_t v_off, uint32_t qkv_rs) {
+    pdl_enter();
+    extern __shared__ __align__(16) float sm[];
+    const uint32_t dpad = RS * kDeltaRows, stride = 3 * dpad + 4, tile_elems = kDeltaTile * stride;
+    const uint32_t h = blockIdx.y;
+    const uint32_t cols_per_cta = kDeltaThreads / RS;
+    const uint32_t r = threadIdx.x % RS, col = blockIdx.x * cols_per_cta + threadIdx.x / RS;
+    const bool live = col < vdim;
+    const uint32_t slot = (uint32_t)ctl_word(ctl, ZG_CTL_SLOT);
+    float* S_g = state + (((size_t)slot * H + h) * dim) * vdim;
+    float S[kDeltaRows];
+#pragma unroll
+    for (int i = 0; i < kDeltaRows; i++) {
+        const uint32_t row = delta_row(RS, r, i);
+        S[i] = (live && row < dim) ? S_g[(size_t)row * vdim + col] : 0.0f;
+    }
+    const float* P = prep + (size_t)h * T * stride;
+    const float* vbase = qkv + v_off + (size_t)h * vdim + col;
+    auto stage = [&](uint32_t t0, float* buf) {       // rows of tokens [t0, min(t0 + tile, T)): one contiguous block
+        const uint32_t n4 = min((uint32_t)kDeltaTile, T - t0) * stride / 4;
+        const float* src = P + (size_t)t0 * stride;
+        for (uint32_t i = threadIdx.x; i < n4; i += kDeltaThreads) cp_async16(buf + 4 * i, src + 4 * i);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    stage(0, sm);
+    float vt[kDeltaTile];
+#pragma unroll
+    for (int tt = 0; tt < kDeltaTile; tt++) vt[tt] = (live && (uint32_t)tt < T) ? vbase[(size_t)tt * qkv_rs] : 0.0f;
+    uint32_t cur = 0;
+    for (uint32_t t0 = 0; t0 < T; t0 += kDeltaTile, cur ^= 1) {
+        const uint32_t nt = min((uint32_t)kDeltaTile, T - t0);
+        const bool more = t0 + kDeltaTile < T;
+        if (more) stage(t0 + kDeltaTile, sm + (cur ^ 1) * tile_elems);   // its last readers passed the barrier that ended the tile before
+        float vn[kDeltaTile];                                             // the next tile's values of this column, in flight during the walk
+#pragma unroll
+        for (int tt = 0; tt < kDeltaTile; tt++)
+            vn[tt] = (live && more && t0 + kDeltaTile + tt < T) ? vbase[(size_t)(t0 + kDeltaTile + tt) * qkv_rs] : 0.0f;
+        if (more) asm volatile("cp.async.wait_group 1;" ::: "memory"); else asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+        const float* tile = sm + cur * tile_elems;
+#pragma unroll
+        for (int tti = 0; tti < kDeltaTile; tti++) {
+            if ((uint32_t)tti >= nt) break;
+            const float* row = tile + tti * stride;
+            float4 k4[4], g4[4];
+            float ks0 = 0.0f, ks1 = 0.0f, qs0 = 0.0f, qs1 = 0.0f;
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                const uint32_t at = (c * RS + r) * 4;
+                k4[c] = *reinterpret_cast<const float4*>(row + at);
+                const float4 q4 = *reinterpret_cast<const float4*>(row + dpad + at);
+                g4[c] = *reinterpret_cast<const float4*>(row + 2 * dpad + at);
+                S[4 * c + 0] *= g4[c].x; S[4 * c + 1] *= g4[c].y; S[4 * c + 2] *= g4[c].z; S[4 * c + 3] *= g4[c].w;
+                ks0 = fmaf(S[4 * c + 0], k4[c].x, ks0); ks1 = fmaf(S[4 * c + 1], k4[c].y, ks1);
+                ks0 = fmaf(S[4 * c + 2], k4[c].z, ks0); ks1 = fmaf(S[4 * c + 3], k4[c].w, ks1);
+                qs0 = fmaf(S[4 * c + 0], q4.x, qs0); qs1 = fmaf(S[4 * c + 1], q4.y, qs1);
+                qs0 = fmaf(S[4 * c + 2], q4.z, qs0); qs1 = fmaf(S[4 * c + 3], q4.w, qs1);
+            }
+            float ks = ks0 + ks1, qs = qs0 + qs1;
+            for (uint32_t o = 1; o < RS; o <<= 1) { ks += __shfl_xor_sync(0xffffffffu, ks, o); qs += __shfl_xor_sync(0xffffffffu, qs, o); }
+            const float u = row[3 * dpad] * (vt[tti] - ks);
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                S[4 * c + 0] = fmaf(k4[c].x, u, S[4 * c + 0]); S[4 * c + 1] = fmaf(k4[c].y, u, S[4 * c + 1]);
+                S[4 * c + 2] = fmaf(k4[c].z, u, S[4 * c + 2]); S[4 * c + 3] = fmaf(k4[c].w, u, S[4 * c + 3]);
+            }
+            if (live && r == 0) dst[((size_t)(t0 + tti) * H + h) * vdim + col] = fmaf(u, row[3 * dpad + 1], qs);
+        }
+#pragma unroll
+        for (int tt = 0; tt < kDeltaTile; tt++) vt[tt] = vn[tt];
+        __syncthreads();                                   // everyone is done with this buffer: the next iteration refills it
+    }
+#pragma unroll
+    for (int i = 0; i < kDeltaRows; i++) {
+        const uint32_t row = delta_row(RS, r, i);
         if (live && row < dim) S_g[(size_t)row * vdim + col] = S[i];
     }
 }
@@ -946,7 +1216,7 @@ uint32_t zg_seq_op_writes(uint32_t tag) {
 // window shares per (token, head) of a WINDOW_ATTENTION step: few pairs and a long window (decode) spread over more CTAs
 static uint32_t attention_splits(const ZgSeqOp& s) {
     const uint32_t pairs = s.n[0] * s.n[1], window = s.n[5];
-    if (s.n[3] % 4 || pairs >= 128 || window < 128) return 1;
+    if (s.n[3] % 4 || pairs >= 128 || window < 128 || (s.n[0] >= (uint32_t)kWaTiledMinTokens && s.n[3] <= 128)) return 1;   // the tiled prefill kernel splits nothing
     uint32_t S = (256 + pairs - 1) / pairs;
     if (S > window / 32) S = window / 32;
     return S < 2 ? 1 : (S > 16 ? 16 : S);
@@ -955,6 +1225,10 @@ size_t zg_seq_op_scratch_elems(const ZgOp& op, float* const* bufs) {
     if (op.tag == ZG_OP_WINDOW_ATTENTION) {
         const uint32_t S = attention_splits(op.u.seq);
         return S > 1 ? (size_t)op.u.seq.n[0] * op.u.seq.n[1] * S * (4 + op.u.seq.n[3]) : 0;
+    }
+    if (op.tag == ZG_OP_DELTA_RULE) {                  // the prepared per-token rows of the prefill form
+        const ZgSeqOp& d = op.u.seq;
+        return d.n[0] >= (uint32_t)kDeltaPrepMinTokens ? (size_t)d.n[0] * d.n[1] * (3 * zg_delta_row_slices(d.n[3]) * kDeltaRows + 4) : 0;
     }
     if (!dense_gemm_enabled() || op.tag != ZG_OP_LINEAR || op.u.seq.n[5] != ZG_W_BF16) return 0;
     const ZgSeqOp& s = op.u.seq;
@@ -1011,7 +1285,18 @@ bool zg_launch_seq_op(ZgCudaCtx* ctx, const ZgOp& op, float* const* bufs, float*
             const size_t width = (size_t)G * dim;
             const bool vec = dim % 4 == 0 && s.off[0] % 4 == 0 && s.n[4] % 4 == 0 && width % 4 == 0 && (reinterpret_cast<uintptr_t>(bufs[s.buf[1]]) & 15) == 0 &&
                              (reinterpret_cast<uintptr_t>(bufs[s.buf[2]]) & 15) == 0;
-            if (vec) {
+            if (vec && s.off[2] % 4 == 0 && T >= kWaTiledMinTokens && dim <= 128) {
+                switch ((dim + 15) / 16) {
+                    case 1: launch_window_attention_tiled<1>(s, bufs, st); break;
+                    case 2: launch_window_attention_tiled<2>(s, bufs, st); break;
+                    case 3: launch_window_attention_tiled<3>(s, bufs, st); break;
+                    case 4: launch_window_attention_tiled<4>(s, bufs, st); break;
+                    case 5: launch_window_attention_tiled<5>(s, bufs, st); break;
+                    case 6: launch_window_attention_tiled<6>(s, bufs, st); break;
+                    case 7: launch_window_attention_tiled<7>(s, bufs, st); break;
+                    default: launch_window_attention_tiled<8>(s, bufs, st); break;
+                }
+            } else if (vec) {
                 const uint32_t CH = dim > 128 ? 2 : 1;
                 uint32_t LK = 1;
                 while (LK * 4 * CH < dim) LK <<= 1;
@@ -1056,7 +1341,16 @@ bool zg_launch_seq_op(ZgCudaCtx* ctx, const ZgOp& op, float* const* bufs, float*
             const uint32_t RS = zg_delta_row_slices(dim), cols = kDeltaThreads / RS;
             const size_t smem = ((size_t)3 * kDeltaTile * RS * kDeltaRows + kDeltaTile) * sizeof(float);
             const dim3 grid((vdim + cols - 1) / cols, H);
-            ZG_SEQ_WDT(s.n[9], {
+            if (scratch && T >= (uint32_t)kDeltaPrepMinTokens) {
+                const uint32_t dpad = RS * kDeltaRows;
+                const size_t walk_smem = (size_t)2 * kDeltaTile * (3 * dpad + 4) * sizeof(float);
+                ZG_SEQ_WDT(s.n[9], launch_pdl(k_delta_prepare<WT>, dim3((T * H + 3) / 4), dim3(128), 0, st, scratch, bufs[s.buf[1]], bufs[s.buf[2]], bufs[s.buf[3]],
+                                              wptr<WT>(bufs, s.buf[5], 0), T, H, G, dim, dpad, s.off[0], s.off[1], s.off[3], s.off[4], s.off[5], s.n[5], s.n[6], s.n[7], s.f[1], s.f[2]));
+                ZG_SEQ_CHECK();
+                if (walk_smem > 48 * 1024) cudaFuncSetAttribute(k_delta_walk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)walk_smem);
+                launch_pdl(k_delta_walk, dim3(grid), dim3(kDeltaThreads), walk_smem, st, bufs[s.buf[0]], bufs[s.buf[1]], scratch, bufs[s.buf[6]], bufs[s.buf[7]], T, H, dim, vdim, RS,
+                           s.off[2], s.n[5]);
+            } else ZG_SEQ_WDT(s.n[9], {
                 if (smem > 48 * 1024) cudaFuncSetAttribute(k_delta_rule<WT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
                 launch_pdl(k_delta_rule<WT>, dim3(grid), dim3(kDeltaThreads), smem, st, bufs[s.buf[0]], bufs[s.buf[1]], bufs[s.buf[2]], bufs[s.buf[3]], wptr<WT>(bufs, s.buf[5], 0), bufs[s.buf[6]],
                                                                   bufs[s.buf[7]], T, H, G, dim, vdim, RS, s.off[0], s.off[1], s.off[2], s.off[3], s.off[4], s.off[5],
