@@ -81,7 +81,8 @@ typedef enum ZgOpTag {
  * LINEAR            dst[m, n] = sum_k src[m, k] W[n, k] (+ bias[n])
  *                   buf 0 dst 1 src 2 W 3 bias | off 0 W 1 bias 2 src 3 dst | n 0 M 1 N 2 K 3 src row stride 4 dst row stride 5 wdt
  * NORM              dst = (res +) norm(src) * w ; kind 0: (x - mean) / sqrt(var + eps), kind 1: x / sqrt(mean(x^2) + eps)
- *                   buf 0 dst 1 src 2 w 3 res | off 0 w | n 0 rows 1 cols 2 kind 3 wdt | f 0 eps
+ *                   with buf 4: also dst2 = norm(dst) * w2 in the same launch (the norm closing a sublayer and the one opening the next)
+ *                   buf 0 dst 1 src 2 w 3 res 4 dst2 5 w2 | off 0 w 1 w2 | n 0 rows 1 cols 2 kind 3 wdt 4 kind of dst2 | f 0 eps
  * WINDOW_ATTENTION  causal attention over the last `window` positions whose keys double as values (one projection, one cache),
  *                   grouped query heads, scores capped smoothly (cap * tanh(s / cap), f1 = 0: off), a per-distance per-head
  *                   additive bias table [window, H] (f32 program buffer), a softmax whose denominator carries an extra 1 (a
@@ -103,6 +104,7 @@ typedef enum ZgOpTag {
  *                   head h is h / (H / G).
  *                   buf 0 dst [T, H * vdim] 1 qkv 2 beta logits 3 a 4 gate logits 5 weights 6 state 7 ctl
  *                   off 0 q 1 k 2 v (columns of a qkv row) 3 beta (column of its row) 4 A_log 5 dt_bias 6 norm_w (weights)
+ *                   7 gate (column of its row)
  *                   n 0 T 1 H 2 G 3 dim 4 vdim 5 qkv row stride 6 beta row stride 7 a row stride 8 gate row stride 9 wdt
  *                   f 0 output-norm eps 1 unit-vector eps 2 q scale
  * ROUTE             s = softmax(logits) over all NE outputs; the `top` largest of s + correction are chosen (ties: lowest

@@ -318,3 +318,17 @@ def test_delta_prefill_walks_prepared_tiles(cuda_backend, layer):
     single = np.concatenate([s.feed("d", [t], [0]) for t in toks])
     assert rel(single, want) < 2 * TOL
     close(s)
+
+
+def test_rows_wider_than_the_norm_kernel_caches(cuda_backend):
+    """Rows of more than 16 x 256 values do not fit the norm kernel's registers: the two-pass form, also for the chained norm
+    that closes one sublayer and opens the next, in single-token and many-token steps."""
+    cfg = config([attention_layer(heads=2, kv_heads=1, dim=8, window=6, mlp=moe(experts=2, identity=1, top=2, ff=8)),
+                  delta_layer(heads=2, kv_heads=1, dim=8, vdim=8, conv=2)], width=4104, vocab=23)
+    W = random_weights(cfg, seed=5)
+    toks = tokens(cfg, 19)
+    want, _ = ref.forward(cfg, as_f64(W), toks)
+    s = open_model(cuda_backend, cfg, W, n_slots=2, max_chunk=16)
+    assert rel(s.feed("p", toks, range(19)), want) < 2 * TOL
+    assert rel(np.concatenate([s.feed("d", [t], [0]) for t in toks]), want) < 2 * TOL
+    close(s)

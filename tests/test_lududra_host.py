@@ -142,7 +142,10 @@ def test_lowering_shape(fake_device):
         tags = [op.tag for op in lp.program.ops]
         assert tags[0] == abi.OP_EMBED and lp.logits_rows == rows and (lp.buf_logits is None) == (head == "none")
         assert tags.count(abi.OP_DELTA_RULE) == 2 and tags.count(abi.OP_WINDOW_ATTENTION) == 1 and tags.count(abi.OP_MOE_FFN) == 1
-        assert tags.count(abi.OP_CAUSAL_CONV) == 2 and tags.count(abi.OP_NORM) == 3 * 2 + 2 + (head != "none")
+        # the first norm stands alone; each of the four closing norms carries the norm that follows it, if one does
+        norms = [op for op in lp.program.ops if op.tag == abi.OP_NORM]
+        assert tags.count(abi.OP_CAUSAL_CONV) == 2 and len(norms) == 1 + 4
+        assert sum(op.u.seq.buf[4] != abi.NO_BUF for op in norms) == 3 + (head != "none")
         ext = {e.buf_idx for e in lp.program.externs}
         assert len(ext) == len(lp.program.externs) == 4 + 4   # weight arenas + state buffers, each once
         assert all(lp.program.buffer_sizes[e.buf_idx] == e.buffer.elems for e in lp.program.externs)

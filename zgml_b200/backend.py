@@ -216,8 +216,11 @@ class DeviceOp:
                              [M, N, K, src_rs or K, dst_rs or N, wdt])
 
     @staticmethod
-    def norm(dst, src, w, w_off, rows, cols, eps, wdt, kind="layer", res=None):
-        return DeviceOp._seq(abi.OP_NORM, [dst, src, w, res], [w_off], [rows, cols, {"layer": 0, "rms": 1}[kind], wdt], [eps])
+    def norm(dst, src, w, w_off, rows, cols, eps, wdt, kind="layer", res=None, then=None, then_w=None, then_w_off=0, then_kind="layer"):
+        """dst = (res +) norm(src; w); with `then`, also then = norm(dst; weights at then_w_off of arena then_w) in the same launch."""
+        kinds = {"layer": 0, "rms": 1}
+        return DeviceOp._seq(abi.OP_NORM, [dst, src, w, res, then, then_w if then is not None else None], [w_off, then_w_off],
+                             [rows, cols, kinds[kind], wdt, kinds[then_kind]], [eps])
 
     @staticmethod
     def window_attention(dst, proj, ring, bias_table, ctl, q_off, k_off, gate_off, T, H, G, dim, proj_rs, window, ring_rows, scale, cap):
@@ -231,9 +234,9 @@ class DeviceOp:
 
     @staticmethod
     def delta_rule(dst, qkv, beta, a, gate, w, state, ctl, q_off, k_off, v_off, beta_off, a_log_off, dt_bias_off, norm_off,
-                   T, H, G, dim, vdim, qkv_rs, beta_rs, a_rs, gate_rs, wdt, norm_eps, unit_eps, q_scale):
+                   T, H, G, dim, vdim, qkv_rs, beta_rs, a_rs, gate_rs, wdt, norm_eps, unit_eps, q_scale, gate_off=0):
         return DeviceOp._seq(abi.OP_DELTA_RULE, [dst, qkv, beta, a, gate, w, state, ctl],
-                             [q_off, k_off, v_off, beta_off, a_log_off, dt_bias_off, norm_off],
+                             [q_off, k_off, v_off, beta_off, a_log_off, dt_bias_off, norm_off, gate_off],
                              [T, H, G, dim, vdim, qkv_rs, beta_rs, a_rs, gate_rs, wdt], [norm_eps, unit_eps, q_scale])
 
     @staticmethod

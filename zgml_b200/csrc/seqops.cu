@@ -113,12 +113,23 @@ template <> __device__ __forceinline__ void wld_vec<float>(const float* p, float
     const float4 v = *reinterpret_cast<const float4*>(p);
     out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
 }
-// The activation rows are staged once per CTA in shared memory (float4 reads, no per-weight global loads); two weight
+// The activation rows are staged once per CTA in shared memory (float4 reads, no per-weight global loads); four weight
 // vectors per lane are in flight per trip.
 template <typename WT, int MR>
 __global__ void k_linear_rows_vec(float* __restrict__ dst, const float* __restrict__ src, const WT* __restrict__ W, const WT* __restrict__ bias,
                                   uint32_t M, uint32_t N, uint32_t K, uint32_t src_rs, uint32_t dst_rs) {
-    pdl_enter();
+    // Weights are constants of the model, so this warp's weight row is pulled toward L2 BEFORE the wait on the predecessor:
+    // in a replayed graph the HBM stream of a matvec starts under the tail of the kernel that produces its input.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    {
+        const uint32_t n0 = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+        if (n0 < N) {
+            const char* wb = reinterpret_cast<const char*>(W + (size_t)n0 * K);
+            for (size_t b = (size_t)(threadIdx.x & 31) * 128; b < (size_t)K * sizeof(WT); b += 32 * 128)
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(wb + b));
+        }
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     constexpr int V = WVec<WT>::n;
     extern __shared__ float xs[];                      // [M][K]
     for (uint32_t e = threadIdx.x; e < M * K; e += blockDim.x) xs[e] = src[(size_t)(e / K) * src_rs + e % K];
@@ -143,6 +154,17 @@ __global__ void k_linear_rows_vec(float* __restrict__ dst, const float* __restri
         }
     };
     uint32_t k = lane * V;
+    for (; k + 96 * V < K; k += 128 * V) {
+        float w0[V], w1[V], w2[V], w3[V];
+        wld_vec<WT>(w + k, w0);
+        wld_vec<WT>(w + k + 32 * V, w1);
+        wld_vec<WT>(w + k + 64 * V, w2);
+        wld_vec<WT>(w + k + 96 * V, w3);
+        fma_vec(w0, k);
+        fma_vec(w1, k + 32 * V);
+        fma_vec(w2, k + 64 * V);
+        fma_vec(w3, k + 96 * V);
+    }
     for (; k + 32 * V < K; k += 64 * V) {
         float w0[V], w1[V];
         wld_vec<WT>(w + k, w0);
@@ -210,30 +232,22 @@ __global__ void __launch_bounds__(256) k_linear_tile(float* __restrict__ dst, co
 }
 
 // ── NORM: one CTA per row ────────────────────────────────────────────────────────────────────────────────────────
+// dst = (res +) norm(src; w) and, when a second destination is given, dst2 = norm(dst; w2) in the same launch: the norm
+// that closes a sublayer (with the residual add) and the norm that opens the next one are one kernel.
 constexpr int kNormCache = 16;   // values a thread keeps: rows up to 16 x blockDim are read from memory once
-template <typename WT>
-__global__ void k_norm(float* __restrict__ dst, const float* __restrict__ src, const WT* __restrict__ w, const float* __restrict__ res,
-                       uint32_t cols, uint32_t kind, float eps) {
-    pdl_enter();
-    __shared__ float sh[32];
-    const size_t row = (size_t)blockIdx.x * cols;
-    const float* x = src + row;
-    const bool cached = cols <= kNormCache * blockDim.x;
-    float v[kNormCache];
+template <bool CACHED, typename WF>
+__device__ __forceinline__ void norm_pass(float* __restrict__ out, const float* __restrict__ x, float (&v)[kNormCache], const float* __restrict__ res,
+                                          uint32_t cols, uint32_t kind, float eps, float* sh, bool keep, WF wfn) {
     float s = 0.0f;
-    if (cached) {
+    if (CACHED) {
 #pragma unroll
-        for (int i = 0; i < kNormCache; i++) {
-            const uint32_t c = threadIdx.x + i * blockDim.x;
-            v[i] = c < cols ? x[c] : 0.0f;
-            s += v[i];
-        }
+        for (int i = 0; i < kNormCache; i++) s += v[i];
     } else {
         for (uint32_t c = threadIdx.x; c < cols; c += blockDim.x) s += x[c];
     }
     const float mean = kind == 0 ? block_sum(s, sh) / (float)cols : 0.0f;
     float q = 0.0f;
-    if (cached) {
+    if (CACHED) {
 #pragma unroll
         for (int i = 0; i < kNormCache; i++) {
             const uint32_t c = threadIdx.x + i * blockDim.x;
@@ -244,16 +258,48 @@ __global__ void k_norm(float* __restrict__ dst, const float* __restrict__ src, c
         for (uint32_t c = threadIdx.x; c < cols; c += blockDim.x) { const float d = x[c] - mean; q = fmaf(d, d, q); }
     }
     const float inv = 1.0f / sqrtf(block_sum(q, sh) / (float)cols + eps);
+    if (CACHED) {
+#pragma unroll
+        for (int i = 0; i < kNormCache; i++) {
+            const uint32_t c = threadIdx.x + i * blockDim.x;
+            if (c < cols) {
+                const float y = (v[i] - mean) * inv * wfn(c);
+                const float o = res ? res[c] + y : y;
+                out[c] = o;
+                if (keep) v[i] = o;
+            }
+        }
+    } else {
+        for (uint32_t c = threadIdx.x; c < cols; c += blockDim.x) {
+            const float y = (x[c] - mean) * inv * wfn(c);
+            out[c] = res ? res[c] + y : y;
+        }
+    }
+}
+template <typename WT>
+__global__ void k_norm(float* __restrict__ dst, const float* __restrict__ src, const WT* __restrict__ w, const float* __restrict__ res,
+                       uint32_t cols, uint32_t kind, float eps, float* __restrict__ dst2, const WT* __restrict__ w2, uint32_t kind2) {
+    pdl_enter();
+    __shared__ float sh[32];
+    const size_t row = (size_t)blockIdx.x * cols;
+    const float* x = src + row;
+    const bool cached = cols <= kNormCache * blockDim.x;
+    float v[kNormCache];
+    auto w1 = [&](uint32_t c) { return wld(w, c); };
+    auto wn = [&](uint32_t c) { return wld(w2, c); };
     if (cached) {
 #pragma unroll
         for (int i = 0; i < kNormCache; i++) {
             const uint32_t c = threadIdx.x + i * blockDim.x;
-            if (c < cols) { const float y = (v[i] - mean) * inv * wld(w, c); dst[row + c] = res ? res[row + c] + y : y; }
+            v[i] = c < cols ? x[c] : 0.0f;
         }
+        norm_pass<true>(dst + row, x, v, res ? res + row : nullptr, cols, kind, eps, sh, dst2 != nullptr, w1);
+        if (dst2) norm_pass<true>(dst2 + row, dst + row, v, nullptr, cols, kind2, eps, sh, false, wn);
     } else {
-        for (uint32_t c = threadIdx.x; c < cols; c += blockDim.x) {
-            const float y = (x[c] - mean) * inv * wld(w, c);
-            dst[row + c] = res ? res[row + c] + y : y;
+        norm_pass<false>(dst + row, x, v, res ? res + row : nullptr, cols, kind, eps, sh, false, w1);
+        if (dst2) {
+            __syncthreads();                           // the row just written is read back by other threads
+            norm_pass<false>(dst2 + row, dst + row, v, nullptr, cols, kind2, eps, sh, false, wn);
         }
     }
 }
@@ -371,12 +417,13 @@ __global__ void k_window_attention_v(float* __restrict__ dst, const float* __res
     constexpr int U = 4;                               // keys in flight per lane group: their loads are issued together
     for (uint32_t j0 = j_begin; j0 < j_end; j0 += KP * U) {
         float4 kvv[U][CH];
-        float d[U];
+        float d[U], bj[U];                             // the distance biases travel with the keys: no load inside the serial softmax update
         bool on[U];
 #pragma unroll
         for (int u = 0; u < U; u++) {
             const uint32_t j = j0 + u * KP + ks;
             on[u] = j < j_end;
+            bj[u] = on[u] ? bias[(size_t)(p - j) * H + h] : 0.0f;
             const float* k = base + (size_t)(j % R) * width;
 #pragma unroll
             for (int c = 0; c < CH; c++)
@@ -396,10 +443,9 @@ __global__ void k_window_attention_v(float* __restrict__ dst, const float* __res
 #pragma unroll
         for (int u = 0; u < U; u++) {
             if (!on[u]) continue;
-            const uint32_t j = j0 + u * KP + ks;
             float sc = d[u] * scale;
             if (cap > 0.0f) sc = cap * tanhf(sc / cap);
-            sc += bias[(size_t)(p - j) * H + h];
+            sc += bj[u];
             if (sc > m) {
                 const float corr = expf(m - sc);        // exp(-inf) = 0 on the first key
                 l *= corr;
@@ -630,18 +676,22 @@ static void launch_window_attention_tiled(const ZgSeqOp& s, float* const* bufs, 
 
 // ── CAUSAL_CONV ──────────────────────────────────────────────────────────────────────────────────────────────────
 template <typename WT>
-__global__ void k_causal_conv(float* __restrict__ dst, const float* __restrict__ src, const WT* __restrict__ w, const float* __restrict__ state,
-                              const float* __restrict__ ctl, uint32_t T, uint32_t C, uint32_t taps, uint32_t src_rs, uint32_t dst_rs, uint32_t act) {
+__global__ void k_causal_conv(float* __restrict__ dst, const float* __restrict__ src, const WT* __restrict__ w, float* state,
+                              const float* __restrict__ ctl, uint32_t T, uint32_t C, uint32_t taps, uint32_t src_rs, uint32_t dst_rs, uint32_t act,
+                              uint32_t advance) {
     pdl_enter();
     const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (e >= (size_t)T * C) return;
     const uint32_t t = (uint32_t)(e / C), c = (uint32_t)(e % C);
-    const float* st = state + (size_t)ctl_word(ctl, ZG_CTL_SLOT) * (taps - 1) * C;
+    float* st = state + (size_t)ctl_word(ctl, ZG_CTL_SLOT) * (taps - 1) * C;
     float y = 0.0f;
     for (uint32_t j = 0; j < taps; j++) {
         const int tau = (int)t - (int)(taps - 1) + (int)j;     // time relative to the step's first token
         const float x = tau >= 0 ? src[(size_t)tau * src_rs + c] : st[(size_t)(tau + (int)(taps - 1)) * C + c];
         y = fmaf(wld(w, (size_t)c * taps + j), x, y);
+        // single-token steps: this thread alone touches the channel's carried inputs, so it also shifts them (input j moves to
+        // row j - 1, which was read one trip earlier)
+        if (advance && j > 0) st[(size_t)(j - 1) * C + c] = x;
     }
     if (act == 1) y = y * sigmoidf_(y);
     dst[(size_t)t * dst_rs + c] = y;
@@ -917,25 +967,65 @@ __global__ void k_route(float* __restrict__ dst, const float* __restrict__ logit
     }
 }
 
-// dot of one weight row with an f32 vector by a whole warp (every lane gets the sum); 16-byte weight loads when aligned
+// dot of one weight row with an f32 vector by a whole warp (every lane gets the sum); 16-byte weight loads when aligned,
+// four of them in flight per lane (a row is streamed once, so what hides HBM latency is the number of independent loads)
+template <typename WT>
+__device__ __forceinline__ float fma_vec4(const float* wv, const float* __restrict__ x, float acc) {
+    constexpr int V = WVec<WT>::n;
+#pragma unroll
+    for (int i = 0; i < V / 4; i++) {
+        const float4 xv = *reinterpret_cast<const float4*>(x + 4 * i);
+        acc = fmaf(xv.x, wv[4 * i], fmaf(xv.y, wv[4 * i + 1], fmaf(xv.z, wv[4 * i + 2], fmaf(xv.w, wv[4 * i + 3], acc))));
+    }
+    return acc;
+}
 template <typename WT>
 __device__ __forceinline__ float warp_dot(const WT* __restrict__ w, const float* __restrict__ x, uint32_t K, uint32_t lane) {
     constexpr int V = WVec<WT>::n;
     float acc = 0.0f;
     if (K % V == 0 && (reinterpret_cast<size_t>(w) & 15) == 0 && (reinterpret_cast<size_t>(x) & 15) == 0) {
-        for (uint32_t k = lane * V; k < K; k += 32 * V) {
-            float wv[V];
-            wld_vec<WT>(w + k, wv);
-#pragma unroll
-            for (int i = 0; i < V / 4; i++) {
-                const float4 xv = *reinterpret_cast<const float4*>(x + k + 4 * i);
-                acc = fmaf(xv.x, wv[4 * i], fmaf(xv.y, wv[4 * i + 1], fmaf(xv.z, wv[4 * i + 2], fmaf(xv.w, wv[4 * i + 3], acc))));
-            }
+        float a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+        uint32_t k = lane * V;
+        for (; k + 96 * V < K; k += 128 * V) {
+            float w0[V], w1[V], w2[V], w3[V];
+            wld_vec<WT>(w + k, w0); wld_vec<WT>(w + k + 32 * V, w1); wld_vec<WT>(w + k + 64 * V, w2); wld_vec<WT>(w + k + 96 * V, w3);
+            acc = fma_vec4<WT>(w0, x + k, acc); a1 = fma_vec4<WT>(w1, x + k + 32 * V, a1);
+            a2 = fma_vec4<WT>(w2, x + k + 64 * V, a2); a3 = fma_vec4<WT>(w3, x + k + 96 * V, a3);
         }
+        for (; k < K; k += 32 * V) {
+            float w0[V];
+            wld_vec<WT>(w + k, w0);
+            acc = fma_vec4<WT>(w0, x + k, acc);
+        }
+        acc = (acc + a1) + (a2 + a3);
     } else {
         for (uint32_t k = lane; k < K; k += 32) acc = fmaf(x[k], wld(w, k), acc);
     }
     return warp_sum(acc);
+}
+// two rows against the same vector, their loads interleaved (the gate and up rows of an expert)
+template <typename WT>
+__device__ __forceinline__ void warp_dot2(const WT* __restrict__ wa, const WT* __restrict__ wb, const float* __restrict__ x, uint32_t K, uint32_t lane,
+                                          float& ra, float& rb) {
+    constexpr int V = WVec<WT>::n;
+    if (K % V == 0 && (reinterpret_cast<size_t>(wa) & 15) == 0 && (reinterpret_cast<size_t>(wb) & 15) == 0 && (reinterpret_cast<size_t>(x) & 15) == 0) {
+        float a0 = 0.0f, a1 = 0.0f, b0 = 0.0f, b1 = 0.0f;
+        uint32_t k = lane * V;
+        for (; k + 32 * V < K; k += 64 * V) {
+            float p0[V], p1[V], q0[V], q1[V];
+            wld_vec<WT>(wa + k, p0); wld_vec<WT>(wb + k, q0); wld_vec<WT>(wa + k + 32 * V, p1); wld_vec<WT>(wb + k + 32 * V, q1);
+            a0 = fma_vec4<WT>(p0, x + k, a0); b0 = fma_vec4<WT>(q0, x + k, b0);
+            a1 = fma_vec4<WT>(p1, x + k + 32 * V, a1); b1 = fma_vec4<WT>(q1, x + k + 32 * V, b1);
+        }
+        for (; k < K; k += 32 * V) {
+            float p0[V], q0[V];
+            wld_vec<WT>(wa + k, p0); wld_vec<WT>(wb + k, q0);
+            a0 = fma_vec4<WT>(p0, x + k, a0); b0 = fma_vec4<WT>(q0, x + k, b0);
+        }
+        ra = warp_sum(a0 + a1); rb = warp_sum(b0 + b1);
+    } else {
+        ra = warp_dot(wa, x, K, lane); rb = warp_dot(wb, x, K, lane);
+    }
 }
 
 // ── MOE_FFN, token-wise form: every (token, choice) pair streams the rows of its expert (decode and short steps) ────────
@@ -956,7 +1046,8 @@ __global__ void k_moe_up(float* __restrict__ y, const float* __restrict__ src, c
     }
     if (f >= ff) return;
     const size_t row = ((size_t)e * ff + f) * D;
-    float g = warp_dot(wg + row, x, D, lane), u = warp_dot(wu + row, x, D, lane);
+    float g, u;
+    warp_dot2(wg + row, wu + row, x, D, lane, g, u);
     g = fminf(g, limit);
     u = fminf(fmaxf(u, -limit), limit);
     if (lane == 0) y[(size_t)pair * ff + f] = g * sigmoidf_(alpha * g) * (u + 1.0f);
@@ -1152,6 +1243,8 @@ bool zg_seq_op_valid(const ZgOp& op, const size_t* elems, size_t n_bufs, char* w
             if (!n || s.n[2] > 1) return fail("norm: shape");
             if (!fits(0, 0, n) || !fits(1, 0, n) || !wfits(2, s.off[0], s.n[1])) return fail("norm: extent");
             if (s.buf[3] != ZG_NO_BUF && !fits(3, 0, n)) return fail("norm: residual extent");
+            if (s.buf[4] != ZG_NO_BUF && (s.n[4] > 1 || !fits(4, 0, n) || !wfits(5, s.off[1], s.n[1]) || s.buf[4] == s.buf[0] || s.buf[4] == s.buf[1] || s.buf[4] == s.buf[3]))
+                return fail("norm: chained norm");
             return true;
         }
         case ZG_OP_WINDOW_ATTENTION: {
@@ -1174,7 +1267,7 @@ bool zg_seq_op_valid(const ZgOp& op, const size_t* elems, size_t n_bufs, char* w
         case ZG_OP_DELTA_RULE: {
             const size_t T = s.n[0], H = s.n[1], G = s.n[2], dim = s.n[3], vdim = s.n[4];
             if (!T || !H || !G || H % G || !dim || !vdim || zg_delta_row_slices((uint32_t)dim) > 32) return fail("delta_rule: shape");
-            if (s.off[0] + G * dim > s.n[5] || s.off[1] + G * dim > s.n[5] || s.off[2] + H * vdim > s.n[5] || s.off[3] + H > s.n[6] || H * dim > s.n[7] || H * vdim > s.n[8])
+            if (s.off[0] + G * dim > s.n[5] || s.off[1] + G * dim > s.n[5] || s.off[2] + H * vdim > s.n[5] || s.off[3] + H > s.n[6] || H * dim > s.n[7] || s.off[7] + H * vdim > s.n[8])
                 return fail("delta_rule: columns");
             if (!fits(0, 0, T * H * vdim) || !fits(1, 0, T * s.n[5]) || !fits(2, 0, T * s.n[6]) || !fits(3, 0, T * s.n[7]) || !fits(4, 0, T * s.n[8]) ||
                 !wfits(5, s.off[4], H) || !wfits(5, s.off[5], H * dim) || !wfits(5, s.off[6], vdim) || !have(6) || elems[s.buf[6]] < H * dim * vdim || !fits(7, 0, ZG_CTL_IDS))
@@ -1203,6 +1296,7 @@ bool zg_seq_op_valid(const ZgOp& op, const size_t* elems, size_t n_bufs, char* w
 // which of buf[0..8) an op writes (bit i); everything else it names is read
 uint32_t zg_seq_op_writes(uint32_t tag) {
     switch (tag) {
+        case ZG_OP_NORM: return 1u | (1u << 4);            // a chained second destination, when named
         case ZG_OP_WINDOW_ATTENTION: return 1u | (1u << 2);
         case ZG_OP_CAUSAL_CONV: return 1u | (1u << 3);
         case ZG_OP_DELTA_RULE: return 1u | (1u << 6);
@@ -1274,7 +1368,9 @@ bool zg_launch_seq_op(ZgCudaCtx* ctx, const ZgOp& op, float* const* bufs, float*
         }
         case ZG_OP_NORM: {
             const float* res = s.buf[3] != ZG_NO_BUF ? bufs[s.buf[3]] : nullptr;
-            ZG_SEQ_WDT(s.n[3], launch_pdl(k_norm<WT>, dim3(s.n[0]), dim3(256), 0, st, bufs[s.buf[0]], bufs[s.buf[1]], wptr<WT>(bufs, s.buf[2], s.off[0]), res, s.n[1], s.n[2], s.f[0]));
+            float* dst2 = s.buf[4] != ZG_NO_BUF ? bufs[s.buf[4]] : nullptr;
+            ZG_SEQ_WDT(s.n[3], launch_pdl(k_norm<WT>, dim3(s.n[0]), dim3(256), 0, st, bufs[s.buf[0]], bufs[s.buf[1]], wptr<WT>(bufs, s.buf[2], s.off[0]), res, s.n[1], s.n[2], s.f[0],
+                                          dst2, dst2 ? wptr<WT>(bufs, s.buf[5], s.off[1]) : nullptr, s.n[4]));
             ZG_SEQ_CHECK();
             return true;
         }
@@ -1328,9 +1424,9 @@ bool zg_launch_seq_op(ZgCudaCtx* ctx, const ZgOp& op, float* const* bufs, float*
             const float* src = bufs[s.buf[1]] + s.off[1];
             const size_t n = (size_t)T * C;
             ZG_SEQ_WDT(s.n[6], launch_pdl(k_causal_conv<WT>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, dst, src, wptr<WT>(bufs, s.buf[2], s.off[0]), bufs[s.buf[3]], bufs[s.buf[4]],
-                                                                                          T, C, taps, s.n[3], s.n[4], s.n[5]));
+                                                                                          T, C, taps, s.n[3], s.n[4], s.n[5], (uint32_t)(T == 1 && taps > 1)));
             ZG_SEQ_CHECK();
-            if (taps > 1) {
+            if (taps > 1 && T > 1) {
                 launch_pdl(k_conv_advance, dim3((C + 127) / 128), dim3(128), 0, st, bufs[s.buf[3]], src, bufs[s.buf[4]], T, C, taps, s.n[3]);
                 ZG_SEQ_CHECK();
             }
@@ -1357,7 +1453,7 @@ bool zg_launch_seq_op(ZgCudaCtx* ctx, const ZgOp& op, float* const* bufs, float*
                                                                   s.n[5], s.n[6], s.n[7], s.f[1], s.f[2]);
             });
             ZG_SEQ_CHECK();
-            ZG_SEQ_WDT(s.n[9], launch_pdl(k_delta_out<WT>, dim3((T * H + 3) / 4), dim3(128), 0, st, bufs[s.buf[0]], bufs[s.buf[4]], wptr<WT>(bufs, s.buf[5], 0), T * H, H, vdim, s.n[8], s.off[6], s.f[0]));
+            ZG_SEQ_WDT(s.n[9], launch_pdl(k_delta_out<WT>, dim3((T * H + 3) / 4), dim3(128), 0, st, bufs[s.buf[0]], bufs[s.buf[4]] + s.off[7], wptr<WT>(bufs, s.buf[5], 0), T * H, H, vdim, s.n[8], s.off[6], s.f[0]));
             ZG_SEQ_CHECK();
             return true;
         }

@@ -13,7 +13,7 @@ attention mixer   [q | k | gate] = W_in h + b in ONE matmul (the checkpoint's q,
                   the values), then the WINDOW_ATTENTION op: window, smooth score cap, per-distance bias (the learned
                   bucket table expanded to one row per distance at load), sink, output gate; then W_o.
 channel_delta     [q | k | v | beta | a1 | g1] = W_in h in ONE matmul, one CAUSAL_CONV (+SiLU) over the q | k | v
-                  columns, the two low-rank second stages (decay and gate), the DELTA_RULE op, then W_o.
+                  columns, the two low-rank second stages (decay and gate) as one block-diagonal matmul, the DELTA_RULE op, then W_o.
 moe               router matmul (f32 activations), ROUTE (softmax over real and identity experts, top-k of the corrected
                   scores, uncorrected weights), MOE_FFN over stacked expert weights.
 """
@@ -159,8 +159,10 @@ class LududraModel:
                 A.add("conv", np.concatenate(convs, 0))
                 a2, g2 = tensors(p + "mix.a2"), tensors(p + "mix.g2")
                 assert a2.shape == (H * dim, ra) and g2.shape == (H * vdim, rg)
-                A.add("a2", a2)
-                A.add("g2", g2)
+                # both low-rank second stages as ONE matmul over the adjacent a1 | g1 columns: [[a2, 0], [0, g2]]
+                ag2 = np.zeros((H * dim + H * vdim, ra + rg), np.float32)
+                ag2[:H * dim, :ra], ag2[H * dim:, ra:] = a2, g2
+                A.add("ag2", ag2)
                 A.add("A_log", tensors(p + "mix.A_log"))
                 A.add("dt_bias", tensors(p + "mix.dt_bias"))
                 A.add("onorm", tensors(p + "mix.norm"))
@@ -269,11 +271,31 @@ class LududraModel:
                 return new(T * D)
             return xs[1] if cur == xs[0] else xs[0]
 
+        # the norm that closes a sublayer (with the residual add) waits for the norm that opens the next one: one launch for both
+        closing: List[tuple] = []
+
+        def close_norm(nx, src, wb, w_off, res):
+            flush()
+            closing.append((nx, src, wb, w_off, res))
+
+        def open_norm(dst, src, wb, w_off):
+            if closing and closing[0][0] == src:
+                nx, y_, cb, c_off, res = closing.pop()
+                ops.append(DeviceOp.norm(nx, y_, cb, c_off, T, D, eps, wdt, res=res, then=dst, then_w=wb, then_w_off=w_off))
+            else:
+                flush()
+                ops.append(DeviceOp.norm(dst, src, wb, w_off, T, D, eps, wdt))
+
+        def flush():
+            if closing:
+                nx, y_, cb, c_off, res = closing.pop()
+                ops.append(DeviceOp.norm(nx, y_, cb, c_off, T, D, eps, wdt, res=res))
+
         for i, L in enumerate(cfg.layers):
             m, meta, A, wb = L["mixer"], self.layer_meta[i], self.arenas[i], wbuf[i]
             H, G, dim, vdim = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
             ni = meta["n_in"]
-            ops.append(DeviceOp.norm(h, x, wb, A.off["norm1"], T, D, eps, wdt))
+            open_norm(h, x, wb, A.off["norm1"])
             if L["type"] == "attention":
                 ops.append(DeviceOp.linear(proj, h, wb, A.off["in"], T, ni, D, wdt, bias=wb, bias_off=A.off["in.b"]))
                 win = m["mask"]["size"]
@@ -289,20 +311,19 @@ class LududraModel:
                 conv = scratch("conv", T * C)
                 tail = ext(pool.buffers[f"l{i}.tail"]) if taps > 1 else ctl   # taps == 1: no carried inputs, the operand is unused
                 ops.append(DeviceOp.causal_conv(conv, proj, wb, A.off["conv"], tail, ctl, T, C, taps, wdt, "silu", src_rs=ni))
-                a = scratch("decay", T * H * dim)
-                g = scratch("gate", T * H * vdim)
-                ops.append(DeviceOp.linear(a, proj, wb, A.off["a2"], T, H * dim, meta["ra"], wdt, src_off=meta["a1_off"], src_rs=ni))
-                ops.append(DeviceOp.linear(g, proj, wb, A.off["g2"], T, H * vdim, meta["rg"], wdt, src_off=meta["g1_off"], src_rs=ni))
-                ops.append(DeviceOp.delta_rule(mix, conv, proj, a, g, wb, ext(pool.buffers[f"l{i}.S"]), ctl,
+                nag = H * dim + H * vdim
+                ag = scratch("decay_gate", T * nag)     # [decay logits | gate logits] per token
+                ops.append(DeviceOp.linear(ag, proj, wb, A.off["ag2"], T, nag, meta["ra"] + meta["rg"], wdt, src_off=meta["a1_off"], src_rs=ni))
+                ops.append(DeviceOp.delta_rule(mix, conv, proj, ag, ag, wb, ext(pool.buffers[f"l{i}.S"]), ctl,
                                                0, G * dim, 2 * G * dim, meta["beta_off"], A.off["A_log"], A.off["dt_bias"], A.off["onorm"],
-                                               T, H, G, dim, vdim, C, ni, H * dim, H * vdim, wdt, eps, UNIT_EPS, dim ** -0.5))
+                                               T, H, G, dim, vdim, C, ni, nag, nag, wdt, eps, UNIT_EPS, dim ** -0.5, gate_off=H * dim))
             ops.append(DeviceOp.linear(y, mix, wb, A.off["o"], T, D, H * vdim, wdt))
             nx = next_x(x)
-            ops.append(DeviceOp.norm(nx, y, wb, A.off["norm1b"], T, D, eps, wdt, res=x))
+            close_norm(nx, y, wb, A.off["norm1b"], x)
             x = nx
             if L["mlp"] is not None:
                 NE, E, ff, top = meta["NE"], meta["E"], meta["ff"], meta["top"]
-                ops.append(DeviceOp.norm(h, x, wb, A.off["norm2"], T, D, eps, wdt))
+                open_norm(h, x, wb, A.off["norm2"])
                 rl, rt = scratch("router", T * NE), scratch("route", T * top * 2)
                 ops.append(DeviceOp.linear(rl, h, wb, A.off["router"], T, NE, D, wdt))
                 ops.append(DeviceOp.route(rt, rl, wb, A.off["correction"], T, NE, top, wdt))
@@ -311,15 +332,16 @@ class LududraModel:
                 moe_op.u.seq.buf[4] = scratch("expert", seq_scratch_elems(moe_op))   # the library knows what its kernels stage
                 ops.append(moe_op)
                 nx = next_x(x)
-                ops.append(DeviceOp.norm(nx, y, wb, A.off["norm2b"], T, D, eps, wdt, res=x))
+                close_norm(nx, y, wb, A.off["norm2b"], x)
                 x = nx
             layer_bufs.append(x)
         logits, rows = None, 0
         if head != "none":
-            ops.append(DeviceOp.norm(h, x, gl, GA.off["final.norm"], T, D, eps, wdt))
+            open_norm(h, x, gl, GA.off["final.norm"])
             rows = T if head == "all" else 1
             logits = new(rows * cfg.vocab)
             ops.append(DeviceOp.linear(logits, h, gl, GA.off["head"], rows, cfg.vocab, D, wdt, src_off=0 if head == "all" else (T - 1) * D))
+        flush()
         prog = DeviceProgram(ops, sizes, uploads, [], externs)
         return LoweredProgram(prog, ctl, logits, rows, layer_bufs if keep_layers else None)
 
