@@ -332,3 +332,18 @@ def test_rows_wider_than_the_norm_kernel_caches(cuda_backend):
     assert rel(s.feed("p", toks, range(19)), want) < 2 * TOL
     assert rel(np.concatenate([s.feed("d", [t], [0]) for t in toks]), want) < 2 * TOL
     close(s)
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_sizes_that_fit_no_vector_path(cuda_backend, dtype):
+    """Width, head sizes, expert width and vocabulary that are multiples of neither 4 nor 8: every kernel's scalar form."""
+    cfg = config([attention_layer(heads=3, kv_heads=1, dim=10, window=9, rel_rows=7, bias_max=30, mlp=moe(experts=3, identity=1, top=2, ff=7)),
+                  delta_layer(heads=2, kv_heads=1, dim=6, vdim=9, conv=3, rank_a=3, rank_g=5, mlp=moe(experts=2, identity=0, top=1, ff=11))],
+                 width=50, vocab=31)
+    W = random_weights(cfg, seed=21, qk_gain=2.0)
+    toks = tokens(cfg, 45)
+    want, _ = ref.forward(cfg, as_f64(W), toks)
+    s = open_model(cuda_backend, cfg, W, dtype, n_slots=2, max_chunk=32)
+    assert rel(s.feed("p", toks, range(45)), want) < tol(dtype)
+    assert rel(np.concatenate([s.feed("d", [t], [0]) for t in toks]), want) < 2 * TOL
+    close(s)

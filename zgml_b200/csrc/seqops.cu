@@ -537,7 +537,7 @@ template <int OC>
 __global__ void __launch_bounds__(kWaThreads, 2)
 k_window_attention_tiled(float* __restrict__ dst, const float* __restrict__ proj, const float* __restrict__ ring, const float* __restrict__ bias,
                          const float* __restrict__ ctl, uint32_t T, uint32_t H, uint32_t G, uint32_t dim, uint32_t proj_rs, uint32_t q_off,
-                         uint32_t g_off, uint32_t window, uint32_t R, float scale, float cap) {
+                         uint32_t g_off, uint32_t window, uint32_t R, float scale, float cap, uint32_t n_sm) {
     pdl_enter();
     constexpr int DH = 16 * OC, KP = DH + 4, PP = kWaBK + 4;
     extern __shared__ __align__(16) float sm[];
@@ -545,7 +545,13 @@ k_window_attention_tiled(float* __restrict__ dst, const float* __restrict__ proj
     float* Ks = Qs + kWaBQ * DH;                       // [64][DH + 4]
     float* Ps = Ks + kWaBK * KP;                       // [64][64 + 4]
     float* Bs = Ps + kWaBQ * PP;                       // [128]
-    const uint32_t h = blockIdx.y, kv = h / (H / G), t0 = blockIdx.x * kWaBQ;
+    // A later query tile walks more key tiles.  Blocks are ranked heaviest first (the block scheduler hands them out in index
+    // order); when the whole grid is resident at once, two CTAs per SM, the second CTA of every SM is taken from the light
+    // end instead, so that each SM's pair carries about the same number of key tiles.
+    uint32_t rank = blockIdx.x;
+    if (gridDim.x <= 2 * n_sm && rank >= n_sm) rank = gridDim.x - 1 - (rank - n_sm);
+    const uint32_t n_tiles = (T + kWaBQ - 1) / kWaBQ;
+    const uint32_t h = rank % H, kv = h / (H / G), t0 = (n_tiles - 1 - rank / H) * kWaBQ;
     const uint32_t tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
     const uint32_t pos0 = (uint32_t)ctl_word(ctl, ZG_CTL_POS), slot = (uint32_t)ctl_word(ctl, ZG_CTL_SLOT);
     const uint32_t nq = min((uint32_t)kWaBQ, T - t0);
@@ -670,8 +676,10 @@ static void launch_window_attention_tiled(const ZgSeqOp& s, float* const* bufs, 
     const size_t smem = ((size_t)kWaBQ * DH + (size_t)kWaBK * (DH + 4) + (size_t)kWaBQ * (kWaBK + 4) + 2 * kWaBK) * sizeof(float);
     static bool once = false;
     if (!once) { cudaFuncSetAttribute(k_window_attention_tiled<OC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); once = true; }
-    launch_pdl(k_window_attention_tiled<OC>, dim3((s.n[0] + kWaBQ - 1) / kWaBQ, s.n[1]), dim3(kWaThreads), smem, st, bufs[s.buf[0]], bufs[s.buf[1]], bufs[s.buf[2]],
-               bufs[s.buf[3]], bufs[s.buf[4]], s.n[0], s.n[1], s.n[2], s.n[3], s.n[4], s.off[0], s.off[2], s.n[5], s.n[6], s.f[0], s.f[1]);
+    static int n_sm = 0;
+    if (!n_sm) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev); if (n_sm <= 0) n_sm = 1; }
+    launch_pdl(k_window_attention_tiled<OC>, dim3(((s.n[0] + kWaBQ - 1) / kWaBQ) * s.n[1]), dim3(kWaThreads), smem, st, bufs[s.buf[0]], bufs[s.buf[1]], bufs[s.buf[2]],
+               bufs[s.buf[3]], bufs[s.buf[4]], s.n[0], s.n[1], s.n[2], s.n[3], s.n[4], s.off[0], s.off[2], s.n[5], s.n[6], s.f[0], s.f[1], (uint32_t)n_sm);
 }
 
 // ── CAUSAL_CONV ──────────────────────────────────────────────────────────────────────────────────────────────────
