@@ -347,3 +347,37 @@ def test_sizes_that_fit_no_vector_path(cuda_backend, dtype):
     assert rel(s.feed("p", toks, range(45)), want) < tol(dtype)
     assert rel(np.concatenate([s.feed("d", [t], [0]) for t in toks]), want) < 2 * TOL
     close(s)
+
+
+def test_trace_replayer_command(cuda_backend, tmp_path):
+    """`bin/trace_run` as a user runs it: a model folder, JSON steps on standard input (whole prompts, portions, single
+    tokens, requests that end and free their slot, a step that wants nothing), logits files per step, `done` lines."""
+    import subprocess
+    from zgml_b200.host.safetensors import write_safetensors
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    W = random_weights(MIXED, seed=14, qk_gain=2.0)
+    public = json.loads(json.dumps(MIXED))
+    for L in public["layers"]:
+        L["mixer"] = {k: v for k, v in L["mixer"].items() if not k.startswith("_")}
+    model = tmp_path / "model"
+    model.mkdir()
+    (model / "config.json").write_text(json.dumps(public))
+    write_safetensors(str(model / "model.safetensors"), W)
+    A, B = tokens(MIXED, 37, 1), tokens(MIXED, 21, 2)
+    wa, wb = ref.forward(MIXED, as_f64(W), A)[0], ref.forward(MIXED, as_f64(W), B)[0]
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": A[:30], "want": [0, 29]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": A[30:32], "want": []}], "end": []},
+             {"step": 2, "entries": [{"id": "a", "tokens": A[32:33], "want": [0]}], "end": []},
+             {"step": 3, "entries": [{"id": "a", "tokens": A[33:], "want": [3, 1]}], "end": ["a"]},
+             {"step": 4, "entries": [{"id": "b", "tokens": B, "want": list(range(21))}], "end": ["b"]}]
+    want = {0: wa[[0, 29]], 2: wa[[32]], 3: wa[[36, 34]], 4: wb}
+    for dtype in ("float32", "bfloat16"):
+        out = tmp_path / dtype
+        p = subprocess.run([os.path.join(root, "bin", "trace_run"), "--model", str(model), "--dtype", dtype, "--out", str(out), "--max-tokens", "64"],
+                           input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
+        assert p.returncode == 0, p.stderr[-2000:]
+        assert [l for l in p.stdout.splitlines() if l.startswith("done ")] == [f"done {i}" for i in range(5)]
+        assert not (out / "1.f32").exists()
+        for i, w in want.items():
+            got = np.fromfile(out / f"{i}.f32", dtype="<f4").reshape(-1, MIXED["vocab"])
+            assert got.shape == w.shape and rel(got, w) < tol(dtype)
