@@ -809,9 +809,18 @@ __global__ void __launch_bounds__(kDeltaThreads) k_delta_rule(
 // cp.async, double buffered, and walks the tokens.  Per token a thread scales its rows by the decay and takes BOTH dot
 // products, with k and with q, in the same pass; one shuffle round reduces them together.  The read-out after the write
 // follows from  o = (g S)^T q + u (k . q), so the state update S <- g S + k u^T leaves the output's critical path.
-// A thread's kDeltaRows rows are four groups of four consecutive rows, group c of slice r at row (c RS + r) 4: the RS slices
+// A thread's kWalkRows rows are groups of four consecutive rows, group c of slice r at row (c RS + r) 4: the RS slices
 // of a column read consecutive float4s of a prepared vector (no bank conflict; the columns of a warp read the same words).
 constexpr int kDeltaPrepMinTokens = 16;
+// The walk keeps 16 rows per thread (four groups of four) and 128 threads per CTA.  (8 rows and 256 threads, two warps per
+// scheduler, was measured slower: 388 against 354 us at 16 heads of 128 x 128 — the per-token dependency chain, which a
+// fourth shuffle step lengthens, is what bounds the kernel, not the empty issue slots.)
+constexpr int kWalkRows = 16, kWalkThreads = 128, kWalkMaxDim = 32 * kWalkRows;
+static uint32_t delta_walk_slices(uint32_t dim) {
+    uint32_t rs = 1;
+    while (rs * kWalkRows < dim) rs <<= 1;
+    return rs;
+}
 __device__ __forceinline__ uint32_t delta_row(uint32_t RS, uint32_t r, int i) { return (((uint32_t)i >> 2) * RS + r) * 4 + ((uint32_t)i & 3); }
 template <typename WT>
 __global__ void k_delta_prepare(float* __restrict__ prep, const float* __restrict__ qkv, const float* __restrict__ betab, const float* __restrict__ ab,
@@ -842,21 +851,22 @@ __global__ void k_delta_prepare(float* __restrict__ prep, const float* __restric
 __device__ __forceinline__ void cp_async16(float* smem_dst, const float* gmem_src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gmem_src) : "memory");
 }
-__global__ void __launch_bounds__(kDeltaThreads) k_delta_walk(float* __restrict__ dst, const float* __restrict__ qkv, const float* __restrict__ prep,
+template <uint32_t RS>                                 // row slices of a column: compile-time, so the shuffle steps unroll
+__global__ void __launch_bounds__(kWalkThreads) k_delta_walk(float* __restrict__ dst, const float* __restrict__ qkv, const float* __restrict__ prep,
                                                                float* __restrict__ state, const float* __restrict__ ctl, uint32_t T, uint32_t H,
-                                                               uint32_t dim, uint32_t vdim, uint32_t RS, uint32_t v_off, uint32_t qkv_rs) {
+                                                               uint32_t dim, uint32_t vdim, uint32_t v_off, uint32_t qkv_rs) {
     pdl_enter();
     extern __shared__ __align__(16) float sm[];
-    const uint32_t dpad = RS * kDeltaRows, stride = 3 * dpad + 4, tile_elems = kDeltaTile * stride;
+    const uint32_t dpad = RS * kWalkRows, stride = 3 * dpad + 4, tile_elems = kDeltaTile * stride;
     const uint32_t h = blockIdx.y;
-    const uint32_t cols_per_cta = kDeltaThreads / RS;
+    const uint32_t cols_per_cta = kWalkThreads / RS;
     const uint32_t r = threadIdx.x % RS, col = blockIdx.x * cols_per_cta + threadIdx.x / RS;
     const bool live = col < vdim;
     const uint32_t slot = (uint32_t)ctl_word(ctl, ZG_CTL_SLOT);
     float* S_g = state + (((size_t)slot * H + h) * dim) * vdim;
-    float S[kDeltaRows];
+    float S[kWalkRows];
 #pragma unroll
-    for (int i = 0; i < kDeltaRows; i++) {
+    for (int i = 0; i < kWalkRows; i++) {
         const uint32_t row = delta_row(RS, r, i);
         S[i] = (live && row < dim) ? S_g[(size_t)row * vdim + col] : 0.0f;
     }
@@ -865,7 +875,7 @@ __global__ void __launch_bounds__(kDeltaThreads) k_delta_walk(float* __restrict_
     auto stage = [&](uint32_t t0, float* buf) {       // rows of tokens [t0, min(t0 + tile, T)): one contiguous block
         const uint32_t n4 = min((uint32_t)kDeltaTile, T - t0) * stride / 4;
         const float* src = P + (size_t)t0 * stride;
-        for (uint32_t i = threadIdx.x; i < n4; i += kDeltaThreads) cp_async16(buf + 4 * i, src + 4 * i);
+        for (uint32_t i = threadIdx.x; i < n4; i += kWalkThreads) cp_async16(buf + 4 * i, src + 4 * i);
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
     stage(0, sm);
@@ -884,14 +894,13 @@ __global__ void __launch_bounds__(kDeltaThreads) k_delta_walk(float* __restrict_
         if (more) asm volatile("cp.async.wait_group 1;" ::: "memory"); else asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();
         const float* tile = sm + cur * tile_elems;
-#pragma unroll
-        for (int tti = 0; tti < kDeltaTile; tti++) {
-            if ((uint32_t)tti >= nt) break;
+        auto token = [&](int tti, float v) {
             const float* row = tile + tti * stride;
-            float4 k4[4], g4[4];
+            const float beta = row[3 * dpad], kq = row[3 * dpad + 1];   // read with the vectors, before the shuffles
+            float4 k4[kWalkRows / 4], g4[kWalkRows / 4];
             float ks0 = 0.0f, ks1 = 0.0f, qs0 = 0.0f, qs1 = 0.0f;
 #pragma unroll
-            for (int c = 0; c < 4; c++) {
+            for (int c = 0; c < kWalkRows / 4; c++) {
                 const uint32_t at = (c * RS + r) * 4;
                 k4[c] = *reinterpret_cast<const float4*>(row + at);
                 const float4 q4 = *reinterpret_cast<const float4*>(row + dpad + at);
@@ -903,21 +912,32 @@ __global__ void __launch_bounds__(kDeltaThreads) k_delta_walk(float* __restrict_
                 qs0 = fmaf(S[4 * c + 2], q4.z, qs0); qs1 = fmaf(S[4 * c + 3], q4.w, qs1);
             }
             float ks = ks0 + ks1, qs = qs0 + qs1;
-            for (uint32_t o = 1; o < RS; o <<= 1) { ks += __shfl_xor_sync(0xffffffffu, ks, o); qs += __shfl_xor_sync(0xffffffffu, qs, o); }
-            const float u = row[3 * dpad] * (vt[tti] - ks);
 #pragma unroll
-            for (int c = 0; c < 4; c++) {
+            for (uint32_t o = 1; o < RS; o <<= 1) { ks += __shfl_xor_sync(0xffffffffu, ks, o); qs += __shfl_xor_sync(0xffffffffu, qs, o); }
+            const float u = beta * (v - ks);
+#pragma unroll
+            for (int c = 0; c < kWalkRows / 4; c++) {
                 S[4 * c + 0] = fmaf(k4[c].x, u, S[4 * c + 0]); S[4 * c + 1] = fmaf(k4[c].y, u, S[4 * c + 1]);
                 S[4 * c + 2] = fmaf(k4[c].z, u, S[4 * c + 2]); S[4 * c + 3] = fmaf(k4[c].w, u, S[4 * c + 3]);
             }
-            if (live && r == 0) dst[((size_t)(t0 + tti) * H + h) * vdim + col] = fmaf(u, row[3 * dpad + 1], qs);
+            if (live && r == 0) dst[((size_t)(t0 + tti) * H + h) * vdim + col] = fmaf(u, kq, qs);
+        };
+        if (nt == (uint32_t)kDeltaTile) {                  // a full tile: straight-line code, nothing between the tokens
+#pragma unroll
+            for (int tti = 0; tti < kDeltaTile; tti++) token(tti, vt[tti]);
+        } else {
+#pragma unroll
+            for (int tti = 0; tti < kDeltaTile; tti++) {
+                if ((uint32_t)tti >= nt) break;
+                token(tti, vt[tti]);
+            }
         }
 #pragma unroll
         for (int tt = 0; tt < kDeltaTile; tt++) vt[tt] = vn[tt];
         __syncthreads();                                   // everyone is done with this buffer: the next iteration refills it
     }
 #pragma unroll
-    for (int i = 0; i < kDeltaRows; i++) {
+    for (int i = 0; i < kWalkRows; i++) {
         const uint32_t row = delta_row(RS, r, i);
         if (live && row < dim) S_g[(size_t)row * vdim + col] = S[i];
     }
@@ -1330,7 +1350,7 @@ size_t zg_seq_op_scratch_elems(const ZgOp& op, float* const* bufs) {
     }
     if (op.tag == ZG_OP_DELTA_RULE) {                  // the prepared per-token rows of the prefill form
         const ZgSeqOp& d = op.u.seq;
-        return d.n[0] >= (uint32_t)kDeltaPrepMinTokens ? (size_t)d.n[0] * d.n[1] * (3 * zg_delta_row_slices(d.n[3]) * kDeltaRows + 4) : 0;
+        return d.n[0] >= (uint32_t)kDeltaPrepMinTokens && d.n[3] <= (uint32_t)kWalkMaxDim ? (size_t)d.n[0] * d.n[1] * (3 * delta_walk_slices(d.n[3]) * kWalkRows + 4) : 0;
     }
     if (!dense_gemm_enabled() || op.tag != ZG_OP_LINEAR || op.u.seq.n[5] != ZG_W_BF16) return 0;
     const ZgSeqOp& s = op.u.seq;
@@ -1445,15 +1465,20 @@ bool zg_launch_seq_op(ZgCudaCtx* ctx, const ZgOp& op, float* const* bufs, float*
             const uint32_t RS = zg_delta_row_slices(dim), cols = kDeltaThreads / RS;
             const size_t smem = ((size_t)3 * kDeltaTile * RS * kDeltaRows + kDeltaTile) * sizeof(float);
             const dim3 grid((vdim + cols - 1) / cols, H);
-            if (scratch && T >= (uint32_t)kDeltaPrepMinTokens) {
-                const uint32_t dpad = RS * kDeltaRows;
+            if (scratch && T >= (uint32_t)kDeltaPrepMinTokens && dim <= (uint32_t)kWalkMaxDim) {
+                const uint32_t WS = delta_walk_slices(dim), dpad = WS * kWalkRows, wcols = kWalkThreads / WS;
                 const size_t walk_smem = (size_t)2 * kDeltaTile * (3 * dpad + 4) * sizeof(float);
                 ZG_SEQ_WDT(s.n[9], launch_pdl(k_delta_prepare<WT>, dim3((T * H + 3) / 4), dim3(128), 0, st, scratch, bufs[s.buf[1]], bufs[s.buf[2]], bufs[s.buf[3]],
                                               wptr<WT>(bufs, s.buf[5], 0), T, H, G, dim, dpad, s.off[0], s.off[1], s.off[3], s.off[4], s.off[5], s.n[5], s.n[6], s.n[7], s.f[1], s.f[2]));
                 ZG_SEQ_CHECK();
-                if (walk_smem > 48 * 1024) cudaFuncSetAttribute(k_delta_walk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)walk_smem);
-                launch_pdl(k_delta_walk, dim3(grid), dim3(kDeltaThreads), walk_smem, st, bufs[s.buf[0]], bufs[s.buf[1]], scratch, bufs[s.buf[6]], bufs[s.buf[7]], T, H, dim, vdim, RS,
-                           s.off[2], s.n[5]);
+#define ZG_WALK(RS_)                                                                                                                            \
+    case RS_:                                                                                                                                   \
+        if (walk_smem > 48 * 1024) cudaFuncSetAttribute(k_delta_walk<RS_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)walk_smem);        \
+        launch_pdl(k_delta_walk<RS_>, dim3((vdim + wcols - 1) / wcols, H), dim3(kWalkThreads), walk_smem, st, bufs[s.buf[0]], bufs[s.buf[1]],   \
+                   scratch, bufs[s.buf[6]], bufs[s.buf[7]], T, H, dim, vdim, s.off[2], s.n[5]);                                                 \
+        break;
+                switch (WS) { ZG_WALK(1) ZG_WALK(2) ZG_WALK(4) ZG_WALK(8) ZG_WALK(16) default: ZG_WALK(32) }
+#undef ZG_WALK
             } else ZG_SEQ_WDT(s.n[9], {
                 if (smem > 48 * 1024) cudaFuncSetAttribute(k_delta_rule<WT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
                 launch_pdl(k_delta_rule<WT>, dim3(grid), dim3(kDeltaThreads), smem, st, bufs[s.buf[0]], bufs[s.buf[1]], bufs[s.buf[2]], bufs[s.buf[3]], wptr<WT>(bufs, s.buf[5], 0), bufs[s.buf[6]],
