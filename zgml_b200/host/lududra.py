@@ -360,7 +360,7 @@ def synthetic_config(width: int, n_layers: int, heads: int, kv_heads: int, dim: 
         mlp = {"kind": "moe", "expert": {"ff": ff, "limit": 7.0}, "router": {"experts": experts, "identity": identity, "top": top}}
         if i % attention_every == attention_every - 1:
             mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "mask": {"size": window}, "bias_max": 4 * window,
-                     "softcap": 50.0, "scale": dim ** -0.5}
+                     "softcap": 30.0, "scale": dim ** -0.5}
             layers.append({"type": "attention", "mixer": mixer, "mlp": mlp})
         else:
             layers.append({"type": "channel_delta", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "conv": conv}, "mlp": mlp})
