@@ -82,6 +82,7 @@ typedef enum ZgOpTag {
  *                   buf 0 dst 1 src 2 W 3 bias | off 0 W 1 bias 2 src 3 dst | n 0 M 1 N 2 K 3 src row stride 4 dst row stride 5 wdt
  * NORM              dst = (res +) norm(src) * w ; kind 0: (x - mean) / sqrt(var + eps), kind 1: x / sqrt(mean(x^2) + eps)
  *                   with buf 4: also dst2 = norm(dst) * w2 in the same launch (the norm closing a sublayer and the one opening the next)
+ *                   w and w2 must be constants of the model (an uploaded arena): they are read before the producing op of src has finished
  *                   buf 0 dst 1 src 2 w 3 res 4 dst2 5 w2 | off 0 w 1 w2 | n 0 rows 1 cols 2 kind 3 wdt 4 kind of dst2 | f 0 eps
  * WINDOW_ATTENTION  causal attention over the last `window` positions whose keys double as values (one projection, one cache),
  *                   grouped query heads, scores capped smoothly (cap * tanh(s / cap), f1 = 0: off), a per-distance per-head

@@ -237,7 +237,7 @@ __global__ void __launch_bounds__(256) k_linear_tile(float* __restrict__ dst, co
 constexpr int kNormCache = 16;   // values a thread keeps: rows up to 16 x blockDim are read from memory once
 template <bool CACHED, typename WF>
 __device__ __forceinline__ void norm_pass(float* __restrict__ out, const float* __restrict__ x, float (&v)[kNormCache], const float* __restrict__ res,
-                                          uint32_t cols, uint32_t kind, float eps, float* sh, bool keep, WF wfn) {
+                                          const float (&rv)[kNormCache], uint32_t cols, uint32_t kind, float eps, float* sh, bool keep, WF wfn) {
     float s = 0.0f;
     if (CACHED) {
 #pragma unroll
@@ -263,15 +263,15 @@ __device__ __forceinline__ void norm_pass(float* __restrict__ out, const float* 
         for (int i = 0; i < kNormCache; i++) {
             const uint32_t c = threadIdx.x + i * blockDim.x;
             if (c < cols) {
-                const float y = (v[i] - mean) * inv * wfn(c);
-                const float o = res ? res[c] + y : y;
+                const float y = (v[i] - mean) * inv * wfn(i, c);
+                const float o = res ? rv[i] + y : y;
                 out[c] = o;
                 if (keep) v[i] = o;
             }
         }
     } else {
         for (uint32_t c = threadIdx.x; c < cols; c += blockDim.x) {
-            const float y = (x[c] - mean) * inv * wfn(c);
+            const float y = (x[c] - mean) * inv * wfn(0, c);
             out[c] = res ? res[c] + y : y;
         }
     }
@@ -279,27 +279,37 @@ __device__ __forceinline__ void norm_pass(float* __restrict__ out, const float* 
 template <typename WT>
 __global__ void k_norm(float* __restrict__ dst, const float* __restrict__ src, const WT* __restrict__ w, const float* __restrict__ res,
                        uint32_t cols, uint32_t kind, float eps, float* __restrict__ dst2, const WT* __restrict__ w2, uint32_t kind2) {
-    pdl_enter();
+    // Rows that fit the registers: the norm weights are constants of the model and are read BEFORE the wait on the predecessor;
+    // the row and the residual are read together right after it, so the kernel has one round of global loads, not three.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     __shared__ float sh[32];
     const size_t row = (size_t)blockIdx.x * cols;
     const float* x = src + row;
     const bool cached = cols <= kNormCache * blockDim.x;
-    float v[kNormCache];
-    auto w1 = [&](uint32_t c) { return wld(w, c); };
-    auto wn = [&](uint32_t c) { return wld(w2, c); };
+    float v[kNormCache], rv[kNormCache], wa[kNormCache], wb[kNormCache];
+    if (cached) {
+#pragma unroll
+        for (int i = 0; i < kNormCache; i++) {
+            const uint32_t c = threadIdx.x + i * blockDim.x;
+            wa[i] = c < cols ? wld(w, c) : 0.0f;
+            wb[i] = (dst2 && c < cols) ? wld(w2, c) : 0.0f;
+        }
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     if (cached) {
 #pragma unroll
         for (int i = 0; i < kNormCache; i++) {
             const uint32_t c = threadIdx.x + i * blockDim.x;
             v[i] = c < cols ? x[c] : 0.0f;
+            rv[i] = (res && c < cols) ? res[row + c] : 0.0f;
         }
-        norm_pass<true>(dst + row, x, v, res ? res + row : nullptr, cols, kind, eps, sh, dst2 != nullptr, w1);
-        if (dst2) norm_pass<true>(dst2 + row, dst + row, v, nullptr, cols, kind2, eps, sh, false, wn);
+        norm_pass<true>(dst + row, x, v, res ? res + row : nullptr, rv, cols, kind, eps, sh, dst2 != nullptr, [&](int i, uint32_t) { return wa[i]; });
+        if (dst2) norm_pass<true>(dst2 + row, dst + row, v, nullptr, rv, cols, kind2, eps, sh, false, [&](int i, uint32_t) { return wb[i]; });
     } else {
-        norm_pass<false>(dst + row, x, v, res ? res + row : nullptr, cols, kind, eps, sh, false, w1);
+        norm_pass<false>(dst + row, x, v, res ? res + row : nullptr, rv, cols, kind, eps, sh, false, [&](int, uint32_t c) { return wld(w, c); });
         if (dst2) {
             __syncthreads();                           // the row just written is read back by other threads
-            norm_pass<false>(dst2 + row, dst + row, v, nullptr, cols, kind2, eps, sh, false, wn);
+            norm_pass<false>(dst2 + row, dst + row, v, nullptr, rv, cols, kind2, eps, sh, false, [&](int, uint32_t c) { return wld(w2, c); });
         }
     }
 }
