@@ -64,7 +64,16 @@ typedef enum ZgOpTag {
     ZG_OP_DELTA_RULE = 19,
     ZG_OP_ROUTE = 20,
     ZG_OP_MOE_FFN = 21,
-    ZG_OP_END = 22
+    ZG_OP_TOKEN_SHIFT = 22,
+    ZG_OP_DEPTH_MIX = 23,
+    ZG_OP_ROTARY = 24,
+    ZG_OP_CACHE_APPEND = 25,
+    ZG_OP_CACHED_ATTENTION = 26,
+    ZG_OP_MAP_COMBINE = 27,
+    ZG_OP_GATE = 28,
+    ZG_OP_HEAD_LINEAR = 29,
+    ZG_OP_POLY_NORM = 30,
+    ZG_OP_END = 31
 } ZgOpTag;
 
 /* Parameter pack of the sequence-model ops.  buf[] are program buffer indices (ZG_NO_BUF: absent), off[] element offsets,
@@ -80,10 +89,15 @@ typedef enum ZgOpTag {
  *                   buf 0 dst 1 ctl 2 table | off 0 table | n 0 T 1 D 2 wdt | f 0 scale
  * LINEAR            dst[m, n] = sum_k src[m, k] W[n, k] (+ bias[n])
  *                   buf 0 dst 1 src 2 W 3 bias | off 0 W 1 bias 2 src 3 dst | n 0 M 1 N 2 K 3 src row stride 4 dst row stride 5 wdt
- * NORM              dst = (res +) norm(src) * w ; kind 0: (x - mean) / sqrt(var + eps), kind 1: x / sqrt(mean(x^2) + eps)
+ * NORM              dst = (res +) norm(src) * w ; kind bit 0 clear: (x - mean) / sqrt(var + eps), set: x / sqrt(mean(x^2) + eps);
+ *                   kind bit 1: the weight is stored around zero and applied as (1 + w); kind bit 2: the result is also
+ *                   multiplied by the gain f1 (a scale of the following product folded into its input)
  *                   with buf 4: also dst2 = norm(dst) * w2 in the same launch (the norm closing a sublayer and the one opening the next)
+ *                   with buf 6 (single-row steps): the last output of the launch then passes a TOKEN_SHIFT (mix at off 2 of the
+ *                   arena of the norm it follows, state buf 6, ctl buf 7) in the same launch
  *                   w and w2 must be constants of the model (an uploaded arena): they are read before the producing op of src has finished
- *                   buf 0 dst 1 src 2 w 3 res 4 dst2 5 w2 | off 0 w 1 w2 | n 0 rows 1 cols 2 kind 3 wdt 4 kind of dst2 | f 0 eps
+ *                   buf 0 dst 1 src 2 w 3 res 4 dst2 5 w2 6 shift state 7 ctl | off 0 w 1 w2 2 shift mix 3 dst | n 0 rows 1 cols 2 kind 3 wdt
+ *                   4 kind of dst2 | f 0 eps 1 gain
  * WINDOW_ATTENTION  causal attention over the last `window` positions whose keys double as values (one projection, one cache),
  *                   grouped query heads, scores capped smoothly (cap * tanh(s / cap), f1 = 0: off), a per-distance per-head
  *                   additive bias table [window, H] (f32 program buffer), a softmax whose denominator carries an extra 1 (a
@@ -108,15 +122,51 @@ typedef enum ZgOpTag {
  *                   7 gate (column of its row)
  *                   n 0 T 1 H 2 G 3 dim 4 vdim 5 qkv row stride 6 beta row stride 7 a row stride 8 gate row stride 9 wdt
  *                   f 0 output-norm eps 1 unit-vector eps 2 q scale
- * ROUTE             s = softmax(logits) over all NE outputs; the `top` largest of s + correction are chosen (ties: lowest
- *                   index); dst[t, c] = {index as int32 bits, s[index]} (weights not renormalised)
+ * ROUTE             mode 0: s = softmax(logits) over all NE outputs; the `top` largest of s + correction are chosen (ties:
+ *                   lowest index); dst[t, c] = {index as int32 bits, s[index]} (weights not renormalised)
+ *                   mode 1: z = logits + correction (a bias); the `top` largest z are chosen (ties: lowest index) and weighted
+ *                   by the softmax over the chosen z alone
  *                   buf 0 dst [T, top, 2] 1 logits 2 correction | off 0 correction 1 logits | n 0 T 1 NE 2 top 3 logits row
- *                   stride 4 wdt
- * MOE_FFN           dst[t] = sum_c weight_c * expert_{index_c}(src[t]); expert e < E: W_down (g * sigmoid(f1 * g) * (u + 1)),
+ *                   stride 4 wdt 5 mode
+ * MOE_FFN           dst[t] = sum_c weight_c * expert_{index_c}(src[t]); expert e < E: W_down (g * sigmoid(f1 * g) * (u + f2)),
  *                   g = min(W_gate x, f0), u = clamp(W_up x, -f0, f0); index >= E: the identity (x itself).  Expert weights
  *                   are stacked [E, ff, D] (gate, up) and [E, D, ff] (down).
  *                   buf 0 dst 1 src 2 route 3 weights 4 scratch [T, top, ff] | off 0 gate 1 up 2 down | n 0 T 1 D 2 ff 3 E
- *                   4 top 5 wdt | f 0 limit 1 alpha */
+ *                   4 top 5 wdt | f 0 limit (INFINITY: none) 1 alpha 2 offset of the up branch
+ * TOKEN_SHIFT       dst[t] = src[t] + (src[t - 1] - src[t]) * mix, element by element; src[-1] is the last row of the previous step
+ *                   (state, external [slots, D], zeros for a fresh slot), and the state becomes src[T - 1].
+ *                   buf 0 dst 1 src 2 mix 3 state 4 ctl | off 0 mix | n 0 T 1 D 2 wdt
+ * DEPTH_MIX         dst[e] = sum_{j < terms} coeff[j] * hist[j * stride + e]: a learned average over the outputs of earlier layers
+ *                   buf 0 dst 1 hist 2 coeff | off 0 coeff | n 0 elements 1 terms 2 stride 3 wdt
+ * ROTARY            rotary positions on `heads` vectors per row, in place or (buf 2) read from another buffer: layout 0 pairs
+ *                   (2i, 2i + 1), layout 1 pairs (i, i + dims / 2); pair i of the token at position p turns by
+ *                   p * base^(-2i / dims).  Angles in f32.
+ *                   buf 0 x 1 ctl 2 src | off 0 column of the first vector 1 its column in src | n 0 T 1 heads 2 head stride
+ *                   3 row stride 4 dims 5 layout 6 src head stride 7 src row stride | f 0 base
+ * CACHE_APPEND      the step's rows join a per-sequence cache (external [slots, R, width]; position p lives in row p mod R).
+ *                   Of the appended columns the first `normed` are RMS-normed with a plain weight (a latent), the next `rot`
+ *                   get the token's rotary position (a key part shared by all heads), the rest is copied.
+ *                   buf 0 cache 1 src 2 ctl 3 norm weight | off 0 src column 1 cache column 2 norm weight
+ *                   n 0 T 1 columns 2 src row stride 3 width 4 R 5 normed 6 rot 7 wdt 8 rotary layout | f 0 eps 1 rotary base
+ * CACHED_ATTENTION  softmax attention of the step's queries over cached keys and values.  A query row holds H * maps vectors
+ *                   of dk (head h, map m at (h * maps + m) * dk); a key row G * maps vectors of dk; a value row G vectors of
+ *                   dv; query (h, m) reads key (h / (H / G), m) and value h / (H / G).  The value cache may be the key cache
+ *                   (a latent that serves as both).  Masks: 0 causal, 1 the last `size` positions, 2 causal inside blocks
+ *                   of `size` positions counted from position 0.  R must cover what the mask can reach plus the step.
+ *                   buf 0 dst [T, H * maps, dv] 1 q 2 key cache 3 value cache 4 ctl
+ *                   off 0 q column 1 key column 2 value column (inside a cache row) 3 mask kind 4 mask size
+ *                   n 0 T 1 H 2 G 3 maps 4 dk 5 dv 6 q row stride 7 key row width 8 value row width 9 R | f 0 score scale
+ * MAP_COMBINE       differential attention's combination of two maps: o = a[.., 0, :] - f0 * a[.., 1, :], then
+ *                   o / sqrt(mean(o^2) + f1) * f2 per (token, head)
+ *                   buf 0 dst [rows, dv] 1 src [rows, 2, dv] | n 0 rows 1 dv | f 0 lambda 1 eps 2 output scale
+ * GATE              dst[t, c] *= sigmoid(gate[t, c / group]), in place (group = dv: one gate per head; 1: per element)
+ *                   buf 0 dst 1 gate | off 0 gate column | n 0 T 1 columns 2 group 3 gate row stride 4 dst row stride
+ * HEAD_LINEAR       a block-diagonal product: dst[t, h, n] = sum_k src[t, h, k] W[h, n, k], W stacked [H, N, K]
+ *                   buf 0 dst 1 src 2 W | off 0 W 1 src column 2 dst column | n 0 T 1 H 2 N 3 K 4 src head stride 5 src row
+ *                   stride 6 dst head stride 7 dst row stride 8 wdt
+ * POLY_NORM         dst[t] = a N(z) + b N(z^2) + c N(z^3) + e with N(v) = v / sqrt(mean(v^2) + f0) over the row, powers taken
+ *                   element by element, (a, b, c, e) four weights; may run in place
+ *                   buf 0 dst 1 src 2 coefficients | off 0 coefficients | n 0 T 1 columns 2 wdt | f 0 eps */
 #define ZG_NO_BUF 0xFFFFFFFFu
 #define ZG_W_F32 0
 #define ZG_W_BF16 1

@@ -32,9 +32,9 @@ class FakeBuffer:
 
 @pytest.fixture
 def fake_device(monkeypatch):
-    import zgml_b200.host.lududra as L
     import zgml_b200.host.state as S
-    monkeypatch.setattr(L, "DeviceBuffer", FakeBuffer)
+    import zgml_b200.host.weights as Wt
+    monkeypatch.setattr(Wt, "DeviceBuffer", FakeBuffer)
     monkeypatch.setattr(S, "DeviceBuffer", FakeBuffer)
 
 

@@ -20,7 +20,11 @@ OP_COUNT = 12
 OP_ALLREDUCE, OP_ALLGATHER = 12, 13   # multi-GPU extensions (need comm_init)
 # sequence-model extensions (ZgSeqOp parameter packs)
 (OP_EMBED, OP_LINEAR, OP_NORM, OP_WINDOW_ATTENTION, OP_CAUSAL_CONV, OP_DELTA_RULE, OP_ROUTE, OP_MOE_FFN) = range(14, 22)
-OP_END = 22
+(OP_TOKEN_SHIFT, OP_DEPTH_MIX, OP_ROTARY, OP_CACHE_APPEND, OP_CACHED_ATTENTION, OP_MAP_COMBINE, OP_GATE, OP_HEAD_LINEAR,
+ OP_POLY_NORM) = range(22, 31)
+OP_END = 31
+MASK_CAUSAL, MASK_WINDOW, MASK_BLOCK = 0, 1, 2
+NORM_LAYER, NORM_RMS, NORM_UNIT_OFFSET, NORM_GAIN = 0, 1, 2, 4
 NO_BUF = 0xFFFFFFFF
 W_F32, W_BF16 = 0, 1
 CTL_POS, CTL_SLOT, CTL_IDS = 0, 1, 8

@@ -216,11 +216,19 @@ class DeviceOp:
                              [M, N, K, src_rs or K, dst_rs or N, wdt])
 
     @staticmethod
-    def norm(dst, src, w, w_off, rows, cols, eps, wdt, kind="layer", res=None, then=None, then_w=None, then_w_off=0, then_kind="layer"):
-        """dst = (res +) norm(src; w); with `then`, also then = norm(dst; weights at then_w_off of arena then_w) in the same launch."""
-        kinds = {"layer": 0, "rms": 1}
-        return DeviceOp._seq(abi.OP_NORM, [dst, src, w, res, then, then_w if then is not None else None], [w_off, then_w_off],
-                             [rows, cols, kinds[kind], wdt, kinds[then_kind]], [eps])
+    def norm(dst, src, w, w_off, rows, cols, eps, wdt, kind="layer", res=None, then=None, then_w=None, then_w_off=0, then_kind="layer",
+             gain=None, shift_state=None, shift_off=0, ctl=None, dst_off=0):
+        """dst = (res +) norm(src; w); with `then`, also then = norm(dst; weights at then_w_off of arena then_w) in the same launch.
+        Kinds: "layer", "rms", and "rms1" (RMS norm whose weight is stored around zero, applied as 1 + w).  `gain` multiplies the
+        result(s); `shift_state` (single-row steps, with `then`) passes `then` through a token shift whose mix lies at shift_off of
+        then_w and whose carried row is that state buffer."""
+        kinds = {"layer": abi.NORM_LAYER, "rms": abi.NORM_RMS, "rms1": abi.NORM_RMS | abi.NORM_UNIT_OFFSET}
+        g = abi.NORM_GAIN if gain is not None else 0       # the gain belongs to the last norm of the launch
+        fused = shift_state is not None
+        return DeviceOp._seq(abi.OP_NORM, [dst, src, w, res, then, then_w if then is not None else None, shift_state, ctl if fused else None],
+                             [w_off, then_w_off, shift_off, dst_off],
+                             [rows, cols, kinds[kind] | (g if then is None else 0), wdt, kinds[then_kind] | (g if then is not None else 0)],
+                             [eps, gain if gain is not None else 0.0])
 
     @staticmethod
     def window_attention(dst, proj, ring, bias_table, ctl, q_off, k_off, gate_off, T, H, G, dim, proj_rs, window, ring_rows, scale, cap):
@@ -240,13 +248,59 @@ class DeviceOp:
                              [T, H, G, dim, vdim, qkv_rs, beta_rs, a_rs, gate_rs, wdt], [norm_eps, unit_eps, q_scale])
 
     @staticmethod
-    def route(dst, logits, w, corr_off, T, n_outputs, top, wdt, logits_off=0, logits_rs=0):
-        return DeviceOp._seq(abi.OP_ROUTE, [dst, logits, w], [corr_off, logits_off], [T, n_outputs, top, logits_rs or n_outputs, wdt])
+    def route(dst, logits, w, corr_off, T, n_outputs, top, wdt, logits_off=0, logits_rs=0, mode="corrected_softmax"):
+        """mode "corrected_softmax": softmax over all outputs, choice by softmax + correction, weights not renormalised;
+        "biased_top": choice by logits + bias, weights = softmax over the chosen biased logits."""
+        return DeviceOp._seq(abi.OP_ROUTE, [dst, logits, w], [corr_off, logits_off],
+                             [T, n_outputs, top, logits_rs or n_outputs, wdt, {"corrected_softmax": 0, "biased_top": 1}[mode]])
 
     @staticmethod
-    def moe_ffn(dst, src, route, w, scratch, gate_off, up_off, down_off, T, D, ff, experts, top, wdt, limit, alpha):
+    def moe_ffn(dst, src, route, w, scratch, gate_off, up_off, down_off, T, D, ff, experts, top, wdt, limit, alpha, up_offset=1.0):
         return DeviceOp._seq(abi.OP_MOE_FFN, [dst, src, route, w, scratch], [gate_off, up_off, down_off],
-                             [T, D, ff, experts, top, wdt], [limit, alpha])
+                             [T, D, ff, experts, top, wdt], [limit, alpha, up_offset])
+
+    @staticmethod
+    def token_shift(dst, src, w, mix_off, state, ctl, T, D, wdt):
+        return DeviceOp._seq(abi.OP_TOKEN_SHIFT, [dst, src, w, state, ctl], [mix_off], [T, D, wdt])
+
+    @staticmethod
+    def depth_mix(dst, hist, w, coeff_off, n, terms, stride, wdt):
+        return DeviceOp._seq(abi.OP_DEPTH_MIX, [dst, hist, w], [coeff_off], [n, terms, stride, wdt])
+
+    @staticmethod
+    def rotary(x, ctl, col, T, heads, head_stride, row_stride, dims, base, layout="pairs", src=None, src_col=0, src_hs=0, src_rs=0):
+        return DeviceOp._seq(abi.OP_ROTARY, [x, ctl, src], [col, src_col],
+                             [T, heads, head_stride, row_stride, dims, {"pairs": 0, "halves": 1}[layout], src_hs, src_rs], [base])
+
+    @staticmethod
+    def cache_append(cache, src, ctl, src_col, cache_col, T, cols, src_rs, width, rows, norm_w=None, norm_off=0, normed=0, eps=0.0, wdt=0,
+                     rot=0, rot_base=0.0, rot_layout="pairs"):
+        return DeviceOp._seq(abi.OP_CACHE_APPEND, [cache, src, ctl, norm_w if normed else None], [src_col, cache_col, norm_off],
+                             [T, cols, src_rs, width, rows, normed, rot, wdt, {"pairs": 0, "halves": 1}[rot_layout]], [eps, rot_base])
+
+    @staticmethod
+    def cached_attention(dst, q, k_cache, v_cache, ctl, q_col, k_col, v_col, T, H, G, maps, dk, dv, q_rs, k_width, v_width, rows, scale,
+                         mask="causal", mask_size=0):
+        kinds = {"causal": abi.MASK_CAUSAL, "window": abi.MASK_WINDOW, "block": abi.MASK_BLOCK}
+        return DeviceOp._seq(abi.OP_CACHED_ATTENTION, [dst, q, k_cache, v_cache, ctl], [q_col, k_col, v_col, kinds[mask], mask_size],
+                             [T, H, G, maps, dk, dv, q_rs, k_width, v_width, rows], [scale])
+
+    @staticmethod
+    def map_combine(dst, src, rows, dv, lam, eps, out_scale):
+        return DeviceOp._seq(abi.OP_MAP_COMBINE, [dst, src], [], [rows, dv], [lam, eps, out_scale])
+
+    @staticmethod
+    def gate(dst, gate, gate_col, T, cols, group, gate_rs, dst_rs=0):
+        return DeviceOp._seq(abi.OP_GATE, [dst, gate], [gate_col], [T, cols, group, gate_rs, dst_rs or cols])
+
+    @staticmethod
+    def head_linear(dst, src, w, w_off, T, H, N, K, wdt, src_col=0, src_hs=0, src_rs=0, dst_col=0, dst_hs=0, dst_rs=0):
+        return DeviceOp._seq(abi.OP_HEAD_LINEAR, [dst, src, w], [w_off, src_col, dst_col],
+                             [T, H, N, K, src_hs or K, src_rs or H * K, dst_hs or N, dst_rs or H * N, wdt])
+
+    @staticmethod
+    def poly_norm(dst, src, w, coeff_off, T, cols, eps, wdt):
+        return DeviceOp._seq(abi.OP_POLY_NORM, [dst, src, w], [coeff_off], [T, cols, wdt], [eps])
 
 
 @dataclass

@@ -26,8 +26,8 @@ def cmd_generate(a) -> int:
     from .host.registry import open_session
     from .host.sampling import Sampler
     be = _backend()
-    s = open_session(be, a.model, a.dtype, max_chunk=a.max_chunk)
     prompt = [int(t) for t in a.prompt.split(",") if t.strip()]
+    s = open_session(be, a.model, a.dtype, max_chunk=a.max_chunk, max_tokens=len(prompt) + a.max_new_tokens)
     out = s.generate(prompt, a.max_new_tokens, Sampler(a.temperature, a.top_k, a.top_p, a.seed))
     print(",".join(str(t) for t in out))
     s.close()
@@ -75,7 +75,7 @@ def main(argv=None) -> int:
     t.add_argument("--model", required=True)
     t.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     t.add_argument("--out", required=True)
-    t.add_argument("--max-tokens", type=int, default=0, help="most tokens live requests hold at any time (sizes nothing here: state is O(window))")
+    t.add_argument("--max-tokens", type=int, default=0, help="most tokens live requests hold at any time: sizes the caches of models that keep every position (0: the model's default)")
     t.add_argument("--slots", type=int, default=4)
     t.add_argument("--max-chunk", type=int, default=256)
     t.set_defaults(fn=cmd_trace_run)

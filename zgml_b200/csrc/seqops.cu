@@ -6,60 +6,11 @@
 //
 // Per-sequence state lives in external program buffers indexed by the state slot of the control buffer; the position of
 // the step's first token comes from the same place, so a captured graph replays unchanged from step to step.
-#include "zg_internal.cuh"
+#include "seq_common.cuh"
 
-#include <cuda_bf16.h>
 #include <stdlib.h>
 
 namespace {
-
-typedef __nv_bfloat16 bf16;
-
-template <typename WT> __device__ __forceinline__ float wld(const WT* w, size_t i);
-template <> __device__ __forceinline__ float wld<float>(const float* w, size_t i) { return w[i]; }
-template <> __device__ __forceinline__ float wld<bf16>(const bf16* w, size_t i) { return __bfloat162float(w[i]); }
-
-__device__ __forceinline__ float warp_sum(float v) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    return v;
-}
-__device__ __forceinline__ float warp_max(float v) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-    return v;
-}
-// sum over the whole block, result in every thread; sh: 32 floats
-__device__ float block_sum(float v, float* sh) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
-    v = warp_sum(v);
-    __syncthreads();
-    if (lane == 0) sh[warp] = v;
-    __syncthreads();
-    float r = 0.0f;
-    for (int i = 0; i < nw; i++) r += sh[i];
-    return r;
-}
-// Programmatic dependent launch (as the framework's other program kernels do): let the next kernel of the stream become
-// resident while this one runs, and hold this one until its predecessor has completed.  Nothing is read before the wait.
-__device__ __forceinline__ void pdl_enter() {
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-}
-template <typename... KArgs, typename... Args>
-inline void launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = g_zg_pdl ? 1 : 0;
-    cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
-}
-__device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf(-z)); }
-__device__ __forceinline__ float softplusf_(float z) { return z > 20.0f ? z : log1pf(expf(z)); }
-__device__ __forceinline__ int ctl_word(const float* ctl, int i) { return reinterpret_cast<const int*>(ctl)[i]; }
 
 // ── EMBED ─────────────────────────────────────────────────────────────────────────────────────────────────────────
 template <typename WT>
@@ -96,22 +47,6 @@ __global__ void k_linear_rows(float* __restrict__ dst, const float* __restrict__
             if (lane == 0) dst[(size_t)m * dst_rs + n] = s + b;
         }
     }
-}
-// 16-byte weight loads (8 bf16 / 4 f32 per lane and trip) when the row start and K allow it
-template <typename WT> struct WVec;
-template <> struct WVec<bf16> { static constexpr int n = 8; };
-template <> struct WVec<float> { static constexpr int n = 4; };
-template <typename WT>
-__device__ __forceinline__ void wld_vec(const WT* p, float* out);
-template <> __device__ __forceinline__ void wld_vec<bf16>(const bf16* p, float* out) {
-    const uint4 v = *reinterpret_cast<const uint4*>(p);
-    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-    for (int i = 0; i < 4; i++) { out[2 * i] = __uint_as_float(u[i] << 16); out[2 * i + 1] = __uint_as_float(u[i] & 0xFFFF0000u); }
-}
-template <> __device__ __forceinline__ void wld_vec<float>(const float* p, float* out) {
-    const float4 v = *reinterpret_cast<const float4*>(p);
-    out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
 }
 // The activation rows are staged once per CTA in shared memory (float4 reads, no per-weight global loads); four weight
 // vectors per lane are in flight per trip.
@@ -245,7 +180,7 @@ __device__ __forceinline__ void norm_pass(float* __restrict__ out, const float* 
     } else {
         for (uint32_t c = threadIdx.x; c < cols; c += blockDim.x) s += x[c];
     }
-    const float mean = kind == 0 ? block_sum(s, sh) / (float)cols : 0.0f;
+    const float mean = (kind & 1u) == 0 ? block_sum(s, sh) / (float)cols : 0.0f;
     float q = 0.0f;
     if (CACHED) {
 #pragma unroll
@@ -276,9 +211,15 @@ __device__ __forceinline__ void norm_pass(float* __restrict__ out, const float* 
         }
     }
 }
+// weight as the norm applies it: stored around zero (kind bit 1) and / or carrying the gain of the product that follows (bit 2)
+__device__ __forceinline__ float norm_weight(float w, uint32_t kind, float gain) {
+    if (kind & 2u) w += 1.0f;
+    return (kind & 4u) ? w * gain : w;
+}
 template <typename WT>
 __global__ void k_norm(float* __restrict__ dst, const float* __restrict__ src, const WT* __restrict__ w, const float* __restrict__ res,
-                       uint32_t cols, uint32_t kind, float eps, float* __restrict__ dst2, const WT* __restrict__ w2, uint32_t kind2) {
+                       uint32_t cols, uint32_t kind, float eps, float* __restrict__ dst2, const WT* __restrict__ w2, uint32_t kind2, float gain,
+                       const WT* __restrict__ shift_mix, float* __restrict__ shift_state, const float* __restrict__ ctl) {
     // Rows that fit the registers: the norm weights are constants of the model and are read BEFORE the wait on the predecessor;
     // the row and the residual are read together right after it, so the kernel has one round of global loads, not three.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -291,8 +232,8 @@ __global__ void k_norm(float* __restrict__ dst, const float* __restrict__ src, c
 #pragma unroll
         for (int i = 0; i < kNormCache; i++) {
             const uint32_t c = threadIdx.x + i * blockDim.x;
-            wa[i] = c < cols ? wld(w, c) : 0.0f;
-            wb[i] = (dst2 && c < cols) ? wld(w2, c) : 0.0f;
+            wa[i] = c < cols ? norm_weight(wld(w, c), kind, gain) : 0.0f;
+            wb[i] = (dst2 && c < cols) ? norm_weight(wld(w2, c), kind2, gain) : 0.0f;
         }
     }
     asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -306,10 +247,21 @@ __global__ void k_norm(float* __restrict__ dst, const float* __restrict__ src, c
         norm_pass<true>(dst + row, x, v, res ? res + row : nullptr, rv, cols, kind, eps, sh, dst2 != nullptr, [&](int i, uint32_t) { return wa[i]; });
         if (dst2) norm_pass<true>(dst2 + row, dst + row, v, nullptr, rv, cols, kind2, eps, sh, false, [&](int i, uint32_t) { return wb[i]; });
     } else {
-        norm_pass<false>(dst + row, x, v, res ? res + row : nullptr, rv, cols, kind, eps, sh, false, [&](int, uint32_t c) { return wld(w, c); });
+        norm_pass<false>(dst + row, x, v, res ? res + row : nullptr, rv, cols, kind, eps, sh, false, [&](int, uint32_t c) { return norm_weight(wld(w, c), kind, gain); });
         if (dst2) {
             __syncthreads();                           // the row just written is read back by other threads
-            norm_pass<false>(dst2 + row, dst + row, v, nullptr, rv, cols, kind2, eps, sh, false, [&](int, uint32_t c) { return wld(w2, c); });
+            norm_pass<false>(dst2 + row, dst + row, v, nullptr, rv, cols, kind2, eps, sh, false, [&](int, uint32_t c) { return norm_weight(wld(w2, c), kind2, gain); });
+        }
+    }
+    // Single-row steps: the token shift of the launch's last output happens here too.  Every thread revisits the columns it
+    // wrote itself, so no barrier is needed; the state keeps the row as it was before the shift.
+    if (shift_state) {
+        float* st = shift_state + (size_t)ctl_word(ctl, ZG_CTL_SLOT) * cols;
+        float* last = dst2 ? dst2 : dst;
+        for (uint32_t c = threadIdx.x; c < cols; c += blockDim.x) {
+            const float h = last[row + c], prev = st[c];
+            st[c] = h;
+            last[row + c] = fmaf(prev - h, wld(shift_mix, c), h);
         }
     }
 }
@@ -971,7 +923,7 @@ __global__ void k_delta_out(float* __restrict__ dst, const float* __restrict__ g
 // ── ROUTE: one warp per token ────────────────────────────────────────────────────────────────────────────────────
 template <typename WT>
 __global__ void k_route(float* __restrict__ dst, const float* __restrict__ logits, const WT* __restrict__ corr, uint32_t T, uint32_t NE, uint32_t top,
-                        uint32_t logits_rs) {
+                        uint32_t logits_rs, uint32_t mode) {
     pdl_enter();
     extern __shared__ float sm[];                      // [warps][NE] choice scores
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -979,14 +931,19 @@ __global__ void k_route(float* __restrict__ dst, const float* __restrict__ logit
     if (t >= T) return;
     const float* z = logits + (size_t)t * logits_rs;
     float* ch = sm + warp * NE;
-    float mx = -INFINITY;
-    for (uint32_t e = lane; e < NE; e += 32) mx = fmaxf(mx, z[e]);
-    mx = warp_max(mx);
-    float sum = 0.0f;
-    for (uint32_t e = lane; e < NE; e += 32) sum += expf(z[e] - mx);
-    const float inv = 1.0f / warp_sum(sum);
-    for (uint32_t e = lane; e < NE; e += 32) ch[e] = expf(z[e] - mx) * inv + wld(corr, e);
+    float mx = -INFINITY, inv = 0.0f;
+    if (mode == 0) {
+        for (uint32_t e = lane; e < NE; e += 32) mx = fmaxf(mx, z[e]);
+        mx = warp_max(mx);
+        float sum = 0.0f;
+        for (uint32_t e = lane; e < NE; e += 32) sum += expf(z[e] - mx);
+        inv = 1.0f / warp_sum(sum);
+        for (uint32_t e = lane; e < NE; e += 32) ch[e] = expf(z[e] - mx) * inv + wld(corr, e);
+    } else {
+        for (uint32_t e = lane; e < NE; e += 32) ch[e] = z[e] + wld(corr, e);   // biased logits choose AND weigh
+    }
     __syncwarp();
+    float first = 0.0f, chosen_sum = 0.0f;             // mode 1 (lane 0): the largest chosen logit and the sum of exp(z - first)
     for (uint32_t c = 0; c < top; c++) {
         float best = -INFINITY; uint32_t bi = 0xFFFFFFFFu;
         for (uint32_t e = lane; e < NE; e += 32) if (ch[e] > best) { best = ch[e]; bi = e; }
@@ -998,10 +955,19 @@ __global__ void k_route(float* __restrict__ dst, const float* __restrict__ logit
         if (lane == 0) {
             float* out = dst + ((size_t)t * top + c) * 2;
             reinterpret_cast<int*>(out)[0] = (int)bi;
-            out[1] = bi < NE ? expf(z[bi] - mx) * inv : 0.0f;
+            if (mode == 0) out[1] = bi < NE ? expf(z[bi] - mx) * inv : 0.0f;
+            else {
+                if (c == 0) first = best;
+                out[1] = bi < NE ? expf(best - first) : 0.0f;
+                chosen_sum += out[1];
+            }
             if (bi < NE) ch[bi] = -INFINITY;
         }
         __syncwarp();
+    }
+    if (mode == 1 && lane == 0) {
+        const float norm = 1.0f / chosen_sum;
+        for (uint32_t c = 0; c < top; c++) dst[((size_t)t * top + c) * 2 + 1] *= norm;
     }
 }
 
@@ -1069,7 +1035,7 @@ __device__ __forceinline__ void warp_dot2(const WT* __restrict__ wa, const WT* _
 // ── MOE_FFN, token-wise form: every (token, choice) pair streams the rows of its expert (decode and short steps) ────────
 template <typename WT>
 __global__ void k_moe_up(float* __restrict__ y, const float* __restrict__ src, const float* __restrict__ route, const WT* __restrict__ wg,
-                         const WT* __restrict__ wu, uint32_t D, uint32_t ff, uint32_t E, uint32_t top, float limit, float alpha, uint32_t stage) {
+                         const WT* __restrict__ wu, uint32_t D, uint32_t ff, uint32_t E, uint32_t top, float limit, float alpha, float uoff, uint32_t stage) {
     pdl_enter();
     const uint32_t pair = blockIdx.y;                  // token * top + choice
     const uint32_t f = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
@@ -1088,7 +1054,7 @@ __global__ void k_moe_up(float* __restrict__ y, const float* __restrict__ src, c
     warp_dot2(wg + row, wu + row, x, D, lane, g, u);
     g = fminf(g, limit);
     u = fminf(fmaxf(u, -limit), limit);
-    if (lane == 0) y[(size_t)pair * ff + f] = g * sigmoidf_(alpha * g) * (u + 1.0f);
+    if (lane == 0) y[(size_t)pair * ff + f] = g * sigmoidf_(alpha * g) * (u + uoff);
 }
 template <typename WT>
 __global__ void k_moe_down(float* __restrict__ dst, const float* __restrict__ src, const float* __restrict__ y, const float* __restrict__ route,
@@ -1177,7 +1143,7 @@ __global__ void k_moe_gather(uint32_t* __restrict__ xs, const float* __restrict_
     }
 }
 __global__ void k_moe_act(uint32_t* __restrict__ yb, const float* __restrict__ g, const float* __restrict__ u, const int* __restrict__ row_pair,
-                          uint32_t ff, uint32_t fp2, float limit, float alpha) {
+                          uint32_t ff, uint32_t fp2, float limit, float alpha, float uoff) {
     const uint32_t r = blockIdx.x;
     const bool live = row_pair[r] >= 0;
     for (uint32_t f2 = threadIdx.x; f2 < fp2; f2 += blockDim.x) {
@@ -1186,7 +1152,7 @@ __global__ void k_moe_act(uint32_t* __restrict__ yb, const float* __restrict__ g
             const uint32_t f = 2 * f2 + i;
             if (live && f < ff) {
                 const float gv = fminf(g[(size_t)r * ff + f], limit), uv = fminf(fmaxf(u[(size_t)r * ff + f], -limit), limit);
-                y[i] = gv * sigmoidf_(alpha * gv) * (uv + 1.0f);
+                y[i] = gv * sigmoidf_(alpha * gv) * (uv + uoff);
             }
         }
         uint32_t v;
@@ -1208,21 +1174,7 @@ __global__ void k_moe_combine(float* __restrict__ dst, const float* __restrict__
     }
 }
 
-template <typename WT> const WT* wptr(float* const* bufs, uint32_t b, uint32_t off) { return reinterpret_cast<const WT*>(bufs[b]) + off; }
-
 }  // namespace
-
-#define ZG_SEQ_CHECK()                                                                                          \
-    do {                                                                                                        \
-        cudaError_t _e = cudaGetLastError();                                                                    \
-        if (_e != cudaSuccess) { zg_set_error("sequence op %u: launch failed: %s", op.tag, cudaGetErrorString(_e)); return false; } \
-        ZG_COUNT_LAUNCH();                                                                                      \
-    } while (0)
-// run `call` with WT = the op's weight type
-#define ZG_SEQ_WDT(wdt, ...)                                                          \
-    do {                                                                              \
-        if ((wdt) == ZG_W_BF16) { typedef bf16 WT; __VA_ARGS__; } else { typedef float WT; __VA_ARGS__; } \
-    } while (0)
 
 static bool dense_gemm_enabled() {
     static const bool enabled = [] { const char* e = getenv("ZG_DENSE_GEMM"); return !(e && e[0] == '0'); }();
@@ -1254,6 +1206,7 @@ uint32_t zg_delta_row_slices(uint32_t dim) {
 
 // Static checks of a sequence op against the program's buffer sizes (f32 slots): shapes, strides and every extent.
 bool zg_seq_op_valid(const ZgOp& op, const size_t* elems, size_t n_bufs, char* why, size_t why_n) {
+    if (op.tag >= ZG_OP_TOKEN_SHIFT) return zg_mix_op_valid(op, elems, n_bufs, why, why_n);
     const ZgSeqOp& s = op.u.seq;
     auto fail = [&](const char* m) { snprintf(why, why_n, "%s", m); return false; };
     auto have = [&](int i) { return s.buf[i] != ZG_NO_BUF && s.buf[i] < n_bufs; };
@@ -1278,11 +1231,13 @@ bool zg_seq_op_valid(const ZgOp& op, const size_t* elems, size_t n_bufs, char* w
         }
         case ZG_OP_NORM: {
             const size_t n = (size_t)s.n[0] * s.n[1];
-            if (!n || s.n[2] > 1) return fail("norm: shape");
-            if (!fits(0, 0, n) || !fits(1, 0, n) || !wfits(2, s.off[0], s.n[1])) return fail("norm: extent");
+            if (!n || s.n[2] > 7) return fail("norm: shape");
+            if (!fits(0, s.off[3], n) || !fits(1, 0, n) || !wfits(2, s.off[0], s.n[1])) return fail("norm: extent");
             if (s.buf[3] != ZG_NO_BUF && !fits(3, 0, n)) return fail("norm: residual extent");
-            if (s.buf[4] != ZG_NO_BUF && (s.n[4] > 1 || !fits(4, 0, n) || !wfits(5, s.off[1], s.n[1]) || s.buf[4] == s.buf[0] || s.buf[4] == s.buf[1] || s.buf[4] == s.buf[3]))
+            if (s.buf[4] != ZG_NO_BUF && (s.n[4] > 7 || !fits(4, 0, n) || !wfits(5, s.off[1], s.n[1]) || s.buf[4] == s.buf[0] || s.buf[4] == s.buf[1] || s.buf[4] == s.buf[3]))
                 return fail("norm: chained norm");
+            if (s.buf[6] != ZG_NO_BUF && (s.n[0] != 1 || !have(6) || elems[s.buf[6]] < s.n[1] || !wfits(s.buf[4] != ZG_NO_BUF ? 5 : 2, s.off[2], s.n[1]) || !fits(7, 0, ZG_CTL_IDS)))
+                return fail("norm: fused token shift (single-row steps)");
             return true;
         }
         case ZG_OP_WINDOW_ATTENTION: {
@@ -1314,7 +1269,7 @@ bool zg_seq_op_valid(const ZgOp& op, const size_t* elems, size_t n_bufs, char* w
         }
         case ZG_OP_ROUTE: {
             const size_t T = s.n[0], NE = s.n[1], top = s.n[2], rs = s.n[3];
-            if (!T || !NE || !top || top > NE || rs < NE || NE > 4096) return fail("route: shape");
+            if (!T || !NE || !top || top > NE || rs < NE || NE > 4096 || s.n[5] > 1) return fail("route: shape");
             if (!fits(0, 0, T * top * 2) || !fits(1, s.off[1], (T - 1) * rs + NE) || !wfits(2, s.off[0], NE)) return fail("route: extent");
             return true;
         }
@@ -1334,12 +1289,12 @@ bool zg_seq_op_valid(const ZgOp& op, const size_t* elems, size_t n_bufs, char* w
 // which of buf[0..8) an op writes (bit i); everything else it names is read
 uint32_t zg_seq_op_writes(uint32_t tag) {
     switch (tag) {
-        case ZG_OP_NORM: return 1u | (1u << 4);            // a chained second destination, when named
+        case ZG_OP_NORM: return 1u | (1u << 4) | (1u << 6);   // a chained second destination and a token-shift state, when named
         case ZG_OP_WINDOW_ATTENTION: return 1u | (1u << 2);
         case ZG_OP_CAUSAL_CONV: return 1u | (1u << 3);
         case ZG_OP_DELTA_RULE: return 1u | (1u << 6);
         case ZG_OP_MOE_FFN: return 1u | (1u << 4);
-        default: return 1u;
+        default: return tag >= ZG_OP_TOKEN_SHIFT ? zg_mix_op_writes(tag) : 1u;
     }
 }
 
@@ -1354,6 +1309,7 @@ static uint32_t attention_splits(const ZgSeqOp& s) {
     return S < 2 ? 1 : (S > 16 ? 16 : S);
 }
 size_t zg_seq_op_scratch_elems(const ZgOp& op, float* const* bufs) {
+    if (op.tag >= ZG_OP_TOKEN_SHIFT) return zg_mix_op_scratch_elems(op);
     if (op.tag == ZG_OP_WINDOW_ATTENTION) {
         const uint32_t S = attention_splits(op.u.seq);
         return S > 1 ? (size_t)op.u.seq.n[0] * op.u.seq.n[1] * S * (4 + op.u.seq.n[3]) : 0;
@@ -1407,8 +1363,10 @@ bool zg_launch_seq_op(ZgCudaCtx* ctx, const ZgOp& op, float* const* bufs, float*
         case ZG_OP_NORM: {
             const float* res = s.buf[3] != ZG_NO_BUF ? bufs[s.buf[3]] : nullptr;
             float* dst2 = s.buf[4] != ZG_NO_BUF ? bufs[s.buf[4]] : nullptr;
-            ZG_SEQ_WDT(s.n[3], launch_pdl(k_norm<WT>, dim3(s.n[0]), dim3(256), 0, st, bufs[s.buf[0]], bufs[s.buf[1]], wptr<WT>(bufs, s.buf[2], s.off[0]), res, s.n[1], s.n[2], s.f[0],
-                                          dst2, dst2 ? wptr<WT>(bufs, s.buf[5], s.off[1]) : nullptr, s.n[4]));
+            float* shift_state = s.buf[6] != ZG_NO_BUF ? bufs[s.buf[6]] : nullptr;
+            ZG_SEQ_WDT(s.n[3], launch_pdl(k_norm<WT>, dim3(s.n[0]), dim3(256), 0, st, bufs[s.buf[0]] + s.off[3], bufs[s.buf[1]], wptr<WT>(bufs, s.buf[2], s.off[0]), res, s.n[1], s.n[2], s.f[0],
+                                          dst2, dst2 ? wptr<WT>(bufs, s.buf[5], s.off[1]) : nullptr, s.n[4], s.f[1],
+                                          shift_state ? wptr<WT>(bufs, s.buf[dst2 ? 5 : 2], s.off[2]) : nullptr, shift_state, shift_state ? bufs[s.buf[7]] : nullptr));
             ZG_SEQ_CHECK();
             return true;
         }
@@ -1503,7 +1461,7 @@ bool zg_launch_seq_op(ZgCudaCtx* ctx, const ZgOp& op, float* const* bufs, float*
         case ZG_OP_ROUTE: {
             const uint32_t T = s.n[0], NE = s.n[1];
             ZG_SEQ_WDT(s.n[4], launch_pdl(k_route<WT>, dim3((T + 3) / 4), dim3(128), 4 * NE * sizeof(float), st, bufs[s.buf[0]], bufs[s.buf[1]] + s.off[1], wptr<WT>(bufs, s.buf[2], s.off[0]), T, NE,
-                                                                                         s.n[2], s.n[3]));
+                                                                                         s.n[2], s.n[3], s.n[5]));
             ZG_SEQ_CHECK();
             return true;
         }
@@ -1521,7 +1479,7 @@ bool zg_launch_seq_op(ZgCudaCtx* ctx, const ZgOp& op, float* const* bufs, float*
                 ZG_SEQ_CHECK();
                 if (!zg_dense_gemm_grouped_launch(wptr<bf16>(bufs, s.buf[3], s.off[0]), E, sc + L.xs, L.R, L.Dp, tile_group, sc + L.g, ff, D, ff, st) ||
                     !zg_dense_gemm_grouped_launch(wptr<bf16>(bufs, s.buf[3], s.off[1]), E, sc + L.xs, L.R, L.Dp, tile_group, sc + L.u, ff, D, ff, st)) return false;
-                k_moe_act<<<L.R, 256, 0, st>>>(reinterpret_cast<uint32_t*>(sc + L.yb), sc + L.g, sc + L.u, row_pair, ff, L.Fp / 2, s.f[0], s.f[1]);
+                k_moe_act<<<L.R, 256, 0, st>>>(reinterpret_cast<uint32_t*>(sc + L.yb), sc + L.g, sc + L.u, row_pair, ff, L.Fp / 2, s.f[0], s.f[1], s.f[2]);
                 ZG_SEQ_CHECK();
                 if (!zg_dense_gemm_grouped_launch(wptr<bf16>(bufs, s.buf[3], s.off[2]), E, sc + L.yb, L.R, L.Fp, tile_group, sc + L.z, D, ff, D, st)) return false;
                 k_moe_combine<<<T, 256, 0, st>>>(bufs[s.buf[0]], bufs[s.buf[1]], sc + L.z, bufs[s.buf[2]], pos_of_pair, D, top);
@@ -1532,7 +1490,7 @@ bool zg_launch_seq_op(ZgCudaCtx* ctx, const ZgOp& op, float* const* bufs, float*
                 if (E && ff) {
                     const uint32_t stage = (size_t)D * 4 <= 48 * 1024 ? 1u : 0u;
                     launch_pdl(k_moe_up<WT>, dim3(dim3((ff + 7) / 8, T * top)), dim3(256), stage ? D * sizeof(float) : 0, st, bufs[s.buf[4]], bufs[s.buf[1]], bufs[s.buf[2]], wptr<WT>(bufs, s.buf[3], s.off[0]),
-                                                                           wptr<WT>(bufs, s.buf[3], s.off[1]), D, ff, E, top, s.f[0], s.f[1], stage);
+                                                                           wptr<WT>(bufs, s.buf[3], s.off[1]), D, ff, E, top, s.f[0], s.f[1], s.f[2], stage);
                     ZG_COUNT_LAUNCH();
                 }
                 launch_pdl(k_moe_down<WT>, dim3(dim3((D + 7) / 8, T)), dim3(256), 0, st, bufs[s.buf[0]], bufs[s.buf[1]], bufs[s.buf[4]], bufs[s.buf[2]], wptr<WT>(bufs, s.buf[3], s.off[2]), D, ff, E, top);
@@ -1541,7 +1499,6 @@ bool zg_launch_seq_op(ZgCudaCtx* ctx, const ZgOp& op, float* const* bufs, float*
             return true;
         }
         default:
-            zg_set_error("unsupported sequence op tag %u", op.tag);
-            return false;
+            return zg_launch_mix_op(op, bufs, scratch, st);
     }
 }

@@ -379,6 +379,11 @@ size_t zg_dense_gemm_scratch_elems(uint32_t M, uint32_t K);
 unsigned int zg_dense_gemm_timeouts();
 bool zg_dense_gemm_grouped_launch(const void* w_bf16, uint32_t groups, const void* xb, uint32_t rows, uint32_t Kp, const int* d_tile_group, float* dst,
                                   uint32_t N, uint32_t K, uint32_t dst_rs, cudaStream_t st);
+// mixops.cu : ZG_OP_TOKEN_SHIFT .. ZG_OP_POLY_NORM, reached through the functions above
+bool zg_mix_op_valid(const ZgOp& op, const size_t* elems, size_t n_bufs, char* why, size_t why_n);
+uint32_t zg_mix_op_writes(uint32_t tag);
+size_t zg_mix_op_scratch_elems(const ZgOp& op);
+bool zg_launch_mix_op(const ZgOp& op, float* const* bufs, float* scratch, cudaStream_t st);
 size_t zg_seq_op_operand_scratch(const ZgOp& op);   // f32 slots an op's own scratch operand needs (MOE_FFN)
 bool zg_dense_gemm_launch(const void* w_bf16, const void* bias_bf16, const float* src, float* dst, uint32_t M, uint32_t N, uint32_t K,
                           uint32_t src_rs, uint32_t dst_rs, float* scratch, cudaStream_t st);

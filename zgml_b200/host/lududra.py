@@ -27,9 +27,10 @@ import numpy as np
 
 from .. import abi
 from ..backend import CudaBackend, DeviceBuffer, DeviceOp, DeviceProgram, ExternBuffer, ProgramIO, seq_scratch_elems
-from .safetensors import SafetensorsFile, f32_to_bf16_bits
+from .safetensors import SafetensorsFile
 from .session import LoweredProgram
 from .state import SequenceStatePool, StateSpec
+from .weights import WeightArena as _Arena
 
 ARCHITECTURE = "Lududra"
 UNIT_EPS = 1e-6          # inside the root of the q / k unit vectors
@@ -86,35 +87,6 @@ def distance_bias_table(rel: np.ndarray, window: int, bias_max: float) -> np.nda
     """[window, heads] f32: the bias of every distance the window can see (what WINDOW_ATTENTION indexes)."""
     rows = [distance_bucket(n, rel.shape[0], bias_max) for n in range(window)]
     return np.ascontiguousarray(rel[rows], dtype=np.float32)
-
-
-class _Arena:
-    """Tensors of one layer packed back to back (16-byte aligned starts) in the session's weight format."""
-
-    def __init__(self, wdt: int):
-        self.wdt = wdt
-        self.parts: List[np.ndarray] = []
-        self.off: Dict[str, int] = {}
-        self.n = 0
-
-    def add(self, name: str, a: np.ndarray) -> int:
-        a = np.ascontiguousarray(a, dtype=np.float32).ravel()
-        pad = -self.n % 8
-        if pad:
-            self.parts.append(np.zeros(pad, np.float32))
-            self.n += pad
-        self.off[name] = self.n
-        self.parts.append(a)
-        self.n += a.size
-        return self.off[name]
-
-    def upload(self, be: CudaBackend) -> DeviceBuffer:
-        flat = np.concatenate(self.parts) if self.parts else np.zeros(8, np.float32)
-        host = f32_to_bf16_bits(flat) if self.wdt == abi.W_BF16 else flat     # checkpoint values are bfloat16: exact either way
-        buf = DeviceBuffer(be, host.nbytes, zero=False)
-        buf.upload(host)
-        self.parts = []
-        return buf
 
 
 class LududraModel:
@@ -214,7 +186,7 @@ class LududraModel:
     def ring_rows(self, window: int, max_chunk: int) -> int:
         return window - 1 + max_chunk
 
-    def state_specs(self, max_chunk: int) -> List[StateSpec]:
+    def state_specs(self, max_chunk: int, max_context: Optional[int] = None) -> List[StateSpec]:   # state is O(window): no bound on positions
         specs = []
         for i, L in enumerate(self.cfg.layers):
             m = L["mixer"]

@@ -2,7 +2,9 @@
 
 A model object provides
   * `vocab`                       — logits per position,
-  * `state_specs(max_chunk)`      — the per-sequence device state it carries between steps (host/state.py),
+  * `state_specs(max_chunk, max_context)` — the per-sequence device state it carries between steps (host/state.py); a model
+                                    that caches every position (`bounded_context`) sizes its caches for `max_context`
+                                    positions, and the session refuses to advance a sequence past them,
   * `lower(T, head, pool)`        — the DeviceProgram that advances one sequence by exactly T tokens from the pool's
                                     state (`head` = "none" | "last" | "all": which positions' logits it produces).
 
@@ -53,11 +55,13 @@ def cut(n: int, menu: Sequence[int]) -> List[int]:
 
 
 class SequenceSession:
-    def __init__(self, be: CudaBackend, model, n_slots: int = 1, max_chunk: int = 256, keep_layers: bool = False):
+    def __init__(self, be: CudaBackend, model, n_slots: int = 1, max_chunk: int = 256, keep_layers: bool = False,
+                 max_context: Optional[int] = None):
         self.be, self.model, self.keep_layers = be, model, keep_layers
         self.menu = chunk_menu(max_chunk)
         self.max_chunk = self.menu[0]
-        self.pool = SequenceStatePool(be, model.state_specs(self.max_chunk), n_slots)
+        self.pool = SequenceStatePool(be, model.state_specs(self.max_chunk, max_context), n_slots)
+        self.context_limit = model.capacity(self.max_chunk, max_context) if getattr(model, "bounded_context", False) else None
         self._programs: Dict[Tuple[int, str], tuple] = {}
         self.executions = 0
 
@@ -94,6 +98,9 @@ class SequenceSession:
         if any(w < 0 or w >= len(tokens) for w in want):
             raise ValueError("wanted place outside the step's tokens")
         slot = self.pool.acquire(request_id)
+        if self.context_limit is not None and self.pool.position(request_id) + len(tokens) > self.context_limit:
+            raise ValueError(f"request {request_id!r} would reach position {self.pool.position(request_id) + len(tokens)}: the session's caches hold "
+                             f"{self.context_limit} positions per sequence")
         rows: Dict[int, np.ndarray] = {}
         at = 0
         for T in cut(len(tokens), self.menu):
