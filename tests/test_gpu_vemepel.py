@@ -262,6 +262,25 @@ def test_far_key_among_hundreds(cuda_backend, layer):
     close(s)
 
 
+@pytest.mark.parametrize("layer", [latent_layer(heads=4, dim=12, vdim=8, kv_rank=320), latent2_layer(heads=3, dim=72, rot_dim=8, vdim=20, kv_rank=136),
+                                   diff_layer(heads=4, kv_heads=2, dim=68, vdim=132, block=290), diff_layer(heads=8, kv_heads=1, dim=4, vdim=4, block=129)],
+                         ids=["latent-rank320", "latent2-dim72", "diff-wide", "diff-8-per-group"])
+def test_wide_heads_and_split_decoding(cuda_backend, layer):
+    """Key and value sizes beyond one 64-wide slice of the tiled kernel (several key slices, two value slices) and caches long
+    enough that single-token steps deal their keys to several CTAs and merge the shares."""
+    cfg = config([layer], width=48, vocab=50)
+    W = random_weights(cfg, seed=18, qk_gain=3.0)
+    n = 300
+    toks = tokens(cfg, n)
+    want = ref.forward(cfg, as_f64(W), toks)
+    s = open_model(cuda_backend, cfg, W, "float32", n_slots=2, max_chunk=128, max_context=512)
+    assert rel(s.feed("p", toks, range(n)), want) < TOL
+    s.feed("d", toks[:n - 12], [])
+    decoded = np.concatenate([s.feed("d", toks[i:i + 1], [0]) for i in range(n - 12, n - 4)] + [s.feed("d", toks[n - 4:], range(4))])
+    assert rel(decoded, want[n - 12:]) < TOL
+    close(s)
+
+
 def test_long_decoding_over_a_small_block_cache(cuda_backend):
     """150 decoded tokens: the block cache of the differential layers (block - 1 + chunk rows) turns over many times while the
     latent caches keep every position."""

@@ -162,6 +162,207 @@ __global__ void k_cached_attention(CaArgs a) {
     }
 }
 
+
+// Tiled form (16-byte aligned shapes): flash tiling in f32.  The query ROWS of a tile are (token, head of the key group)
+// pairs, so the heads that share a key head — all heads of a latent attention, the group of a grouped one — meet every key
+// tile once, in a prompt (64 rows = 64 / heads-per-group tokens) and in decoding alike (a few tokens x the group's heads).
+// One CTA owns 64 rows of one (key head, map) and one slice of up to 16 OC value columns, and walks the key tiles its rows'
+// masks reach: the scores accumulate over 64-wide slices of the key dimension (any dk), thread (ty, tx) of 16 x 16 holding
+// rows 4 ty .. 4 ty + 3 against keys tx + 16 c; the row statistics of the running softmax are shared through half-warp
+// shuffles, the probabilities pass through shared memory, value columns tx + 16 c accumulate in registers.  With `splits`
+// > 1 (few rows, long caches: decoding) the key tiles are dealt to gridDim.z CTAs, each leaving (max, sum, unnormalised
+// output) per row for k_cached_attention_merge.
+constexpr int kCtBQ = 64, kCtBK = 64, kCtDS = 64, kCtThreads = 256, kCtMaxSplits = 32;
+template <int OC>
+__global__ void __launch_bounds__(kCtThreads) k_cached_attention_tiled(CaArgs a, uint32_t rh, uint32_t n_tiles, uint32_t splits, float* __restrict__ part) {
+    pdl_enter();
+    constexpr int DV = 16 * OC, KP = kCtDS + 4, PP = kCtBK + 4;
+    extern __shared__ __align__(16) float sm[];
+    float* Qs = sm;                                    // [64][64]
+    float* Ks = Qs + kCtBQ * kCtDS;                    // [64][64 + 4]
+    float* Ps = Ks + kCtBK * KP;                       // [64][64 + 4]
+    float* Vs = Ps + kCtBQ * PP;                       // [64][DV]
+    const uint32_t tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    const uint32_t n_vs = (a.dv + DV - 1) / DV;
+    const uint32_t tile = n_tiles - 1 - blockIdx.x;    // later rows walk more keys: heaviest first
+    const uint32_t gm = blockIdx.y / n_vs, vs = blockIdx.y % n_vs, g = gm / a.maps, m = gm % a.maps;
+    const uint32_t pos0 = (uint32_t)ctl_word(a.ctl, ZG_CTL_POS), slot = (uint32_t)ctl_word(a.ctl, ZG_CTL_SLOT);
+    const uint32_t total = a.T * rh, r0 = tile * kCtBQ, nq = min((uint32_t)kCtBQ, total - r0);
+    const uint32_t p_min = pos0 + r0 / rh, p_max = pos0 + (r0 + nq - 1) / rh;
+    const uint32_t k_lo = mask_low(p_min, a.kind, a.size);
+    const uint32_t n_kt = (p_max - k_lo) / kCtBK + 1, per = (n_kt + splits - 1) / splits;
+    const uint32_t kt_begin = blockIdx.z * per, kt_end = min(n_kt, kt_begin + per);
+    const float* kbase = a.kc + (size_t)slot * a.R * a.kw + a.k_off + (size_t)gm * a.dk;
+    const float* vbase = a.vc + (size_t)slot * a.R * a.vw + a.v_off + (size_t)g * a.dv + (size_t)vs * DV;
+    const uint32_t v_cols = min((uint32_t)DV, a.dv - vs * DV);
+    uint32_t p_r[4], lo_r[4];
+    bool ok_r[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const uint32_t r = r0 + 4 * ty + i;
+        ok_r[i] = r < total;
+        p_r[i] = pos0 + (ok_r[i] ? r / rh : 0);
+        lo_r[i] = mask_low(p_r[i], a.kind, a.size);
+    }
+    auto load_q = [&](uint32_t d0) {
+        for (uint32_t i = tid; i < kCtBQ * (kCtDS / 4); i += kCtThreads) {
+            const uint32_t rr = i / (kCtDS / 4), c4 = i % (kCtDS / 4), r = r0 + rr;
+            float4 val = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (r < total && d0 + 4 * c4 < a.dk)
+                val = *reinterpret_cast<const float4*>(a.q + (size_t)(r / rh) * a.q_rs + a.q_off + (size_t)((g * rh + r % rh) * a.maps + m) * a.dk + d0 + 4 * c4);
+            *reinterpret_cast<float4*>(Qs + rr * kCtDS + 4 * c4) = val;
+        }
+    };
+    const bool q_once = a.dk <= (uint32_t)kCtDS;
+    if (q_once) load_q(0);
+    float o[4][OC], m_run[4], l_run[4];
+#pragma unroll
+    for (int r = 0; r < 4; r++) {
+        m_run[r] = -INFINITY; l_run[r] = 0.0f;
+#pragma unroll
+        for (int c = 0; c < OC; c++) o[r][c] = 0.0f;
+    }
+    for (uint32_t kt = kt_begin; kt < kt_end; kt++) {
+        const uint32_t s0 = k_lo + kt * kCtBK;
+        float sc[4][4];
+#pragma unroll
+        for (int r = 0; r < 4; r++)
+#pragma unroll
+            for (int c = 0; c < 4; c++) sc[r][c] = 0.0f;
+        for (uint32_t d0 = 0; d0 < a.dk; d0 += kCtDS) {
+            __syncthreads();                           // the previous slice's (or tile's) readers of Qs / Ks / Ps / Vs are done
+            if (!q_once) load_q(d0);
+            for (uint32_t i = tid; i < kCtBK * (kCtDS / 4); i += kCtThreads) {
+                const uint32_t rr = i / (kCtDS / 4), c4 = i % (kCtDS / 4);
+                float4 val = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (s0 + rr <= p_max && d0 + 4 * c4 < a.dk) val = *reinterpret_cast<const float4*>(kbase + (size_t)((s0 + rr) % a.R) * a.kw + d0 + 4 * c4);
+                *reinterpret_cast<float4*>(Ks + rr * KP + 4 * c4) = val;
+            }
+            if (d0 == 0) {
+                for (uint32_t i = tid; i < kCtBK * (DV / 4); i += kCtThreads) {
+                    const uint32_t rr = i / (DV / 4), c4 = i % (DV / 4);
+                    float4 val = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (s0 + rr <= p_max && 4 * c4 < v_cols) val = *reinterpret_cast<const float4*>(vbase + (size_t)((s0 + rr) % a.R) * a.vw + 4 * c4);
+                    *reinterpret_cast<float4*>(Vs + rr * DV + 4 * c4) = val;
+                }
+            }
+            __syncthreads();
+            const uint32_t dn = min((uint32_t)kCtDS, a.dk - d0);
+#pragma unroll 2
+            for (uint32_t d = 0; d < dn; d += 4) {
+                float4 qa[4], ka[4];
+#pragma unroll
+                for (int r = 0; r < 4; r++) qa[r] = *reinterpret_cast<const float4*>(Qs + (4 * ty + r) * kCtDS + d);
+#pragma unroll
+                for (int c = 0; c < 4; c++) ka[c] = *reinterpret_cast<const float4*>(Ks + (tx + 16 * c) * KP + d);
+#pragma unroll
+                for (int r = 0; r < 4; r++)
+#pragma unroll
+                    for (int c = 0; c < 4; c++) {
+                        sc[r][c] = fmaf(qa[r].x, ka[c].x, sc[r][c]); sc[r][c] = fmaf(qa[r].y, ka[c].y, sc[r][c]);
+                        sc[r][c] = fmaf(qa[r].z, ka[c].z, sc[r][c]); sc[r][c] = fmaf(qa[r].w, ka[c].w, sc[r][c]);
+                    }
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < 4; r++) {
+            const uint32_t row = 4 * ty + r;
+            float rmax = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                const uint32_t j = s0 + tx + 16 * c;
+                const float sv = (ok_r[r] && j <= p_r[r] && j >= lo_r[r]) ? sc[r][c] * a.scale : -INFINITY;
+                sc[r][c] = sv;
+                rmax = fmaxf(rmax, sv);
+            }
+#pragma unroll
+            for (int off = 8; off > 0; off >>= 1) rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, off));
+            const float new_m = fmaxf(m_run[r], rmax);
+            const float alpha = m_run[r] == -INFINITY ? (new_m == -INFINITY ? 1.0f : 0.0f) : expf(m_run[r] - new_m);
+            float rsum = 0.0f;
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                const float pv = sc[r][c] == -INFINITY ? 0.0f : expf(sc[r][c] - new_m);
+                Ps[row * PP + tx + 16 * c] = pv;
+                rsum += pv;
+            }
+#pragma unroll
+            for (int off = 8; off > 0; off >>= 1) rsum += __shfl_xor_sync(0xffffffffu, rsum, off);
+            l_run[r] = l_run[r] * alpha + rsum;
+            m_run[r] = new_m;
+#pragma unroll
+            for (int c = 0; c < OC; c++) o[r][c] *= alpha;
+        }
+        __syncthreads();
+#pragma unroll 4
+        for (int j = 0; j < kCtBK; j++) {
+            float pj[4], vj[OC];
+#pragma unroll
+            for (int r = 0; r < 4; r++) pj[r] = Ps[(4 * ty + r) * PP + j];
+#pragma unroll
+            for (int c = 0; c < OC; c++) vj[c] = Vs[j * DV + tx + 16 * c];
+#pragma unroll
+            for (int r = 0; r < 4; r++)
+#pragma unroll
+                for (int c = 0; c < OC; c++) o[r][c] = fmaf(pj[r], vj[c], o[r][c]);
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < 4; r++) {
+        const uint32_t row = r0 + 4 * ty + r;
+        if (!ok_r[r]) continue;
+        const uint32_t hm = (g * rh + row % rh) * a.maps + m;
+        if (splits == 1) {
+            const float inv = 1.0f / l_run[r];         // every query sees itself
+            float* out = a.dst + ((size_t)(row / rh) * a.H * a.maps + hm) * a.dv + (size_t)vs * DV;
+#pragma unroll
+            for (int c = 0; c < OC; c++) if (tx + 16 * c < v_cols) out[tx + 16 * c] = o[r][c] * inv;
+        } else {
+            float* mine = part + (((size_t)(row / rh) * a.H * a.maps + hm) * splits + blockIdx.z) * (4 + a.dv);
+            if (tx == 0 && vs == 0) { mine[0] = m_run[r]; mine[1] = l_run[r]; }
+#pragma unroll
+            for (int c = 0; c < OC; c++) if (tx + 16 * c < v_cols) mine[4 + (size_t)vs * DV + tx + 16 * c] = o[r][c];
+        }
+    }
+}
+// merge of the key shares: one CTA per (token, head, map)
+__global__ void k_cached_attention_merge(float* __restrict__ dst, const float* __restrict__ part, uint32_t dv, uint32_t splits) {
+    pdl_enter();
+    const float* P = part + (size_t)blockIdx.x * splits * (4 + dv);
+    float M = -INFINITY;
+    for (uint32_t i = 0; i < splits; i++) M = fmaxf(M, P[i * (4 + dv)]);
+    float L = 0.0f;
+    for (uint32_t i = 0; i < splits; i++) { const float mi = P[i * (4 + dv)]; if (mi != -INFINITY) L += P[i * (4 + dv) + 1] * expf(mi - M); }
+    const float inv = 1.0f / L;
+    for (uint32_t c = threadIdx.x; c < dv; c += blockDim.x) {
+        float acc = 0.0f;
+        for (uint32_t i = 0; i < splits; i++) { const float mi = P[i * (4 + dv)]; if (mi != -INFINITY) acc = fmaf(P[i * (4 + dv) + 4 + c], expf(mi - M), acc); }
+        dst[(size_t)blockIdx.x * dv + c] = acc * inv;
+    }
+}
+template <int OC>
+static void launch_cached_attention_tiled(const CaArgs& a, uint32_t splits, float* part, cudaStream_t st) {
+    constexpr int DV = 16 * OC;
+    const size_t smem = ((size_t)kCtBQ * kCtDS + (size_t)kCtBK * (kCtDS + 4) + (size_t)kCtBQ * (kCtBK + 4) + (size_t)kCtBK * DV) * sizeof(float);
+    static bool once = false;
+    if (!once) { cudaFuncSetAttribute(k_cached_attention_tiled<OC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); once = true; }
+    const uint32_t rh = a.H / a.G, n_tiles = (a.T * rh + kCtBQ - 1) / kCtBQ, n_vs = (a.dv + DV - 1) / DV;
+    launch_pdl(k_cached_attention_tiled<OC>, dim3(n_tiles, a.G * a.maps * n_vs, splits), dim3(kCtThreads), smem, st, a, rh, n_tiles, splits, part);
+}
+static bool ca_aligned(const ZgSeqOp& s) {
+    return s.n[4] % 4 == 0 && s.n[5] % 4 == 0 && s.n[6] % 4 == 0 && s.n[7] % 4 == 0 && s.n[8] % 4 == 0 && s.off[0] % 4 == 0 && s.off[1] % 4 == 0 && s.off[2] % 4 == 0;
+}
+// key shares per row tile: few CTAs and a long cache (decoding) spread over more of them
+static uint32_t ca_splits(const ZgSeqOp& s) {
+    if (!ca_aligned(s)) return 1;
+    const uint32_t rh = s.n[1] / s.n[2], n_tiles = (s.n[0] * rh + kCtBQ - 1) / kCtBQ, dvs = s.n[5] > 128 ? 256 : 128;
+    const uint32_t ctas = n_tiles * s.n[2] * s.n[3] * ((s.n[5] + dvs - 1) / dvs);
+    const uint32_t reach = s.off[3] ? min(s.n[9], s.off[4] + s.n[0]) : s.n[9];     // keys a row can see at most
+    uint32_t S = 296 / (ctas ? ctas : 1), most = reach / 128;
+    if (S > most) S = most;
+    return S < 2 ? 1 : (S > (uint32_t)kCtMaxSplits ? (uint32_t)kCtMaxSplits : S);
+}
+
 // ── MAP_COMBINE: one warp per (token, head) ──────────────────────────────────────────────────────────────────────
 __global__ void k_map_combine(float* __restrict__ dst, const float* __restrict__ src, uint32_t rows, uint32_t dv, float lambda, float eps, float out_scale) {
     pdl_enter();
@@ -374,8 +575,10 @@ uint32_t zg_mix_op_writes(uint32_t tag) {
 }
 
 size_t zg_mix_op_scratch_elems(const ZgOp& op) {
-    (void)op;
-    return 0;
+    if (op.tag != ZG_OP_CACHED_ATTENTION) return 0;
+    const ZgSeqOp& s = op.u.seq;
+    const uint32_t S = ca_splits(s);
+    return S > 1 ? (size_t)s.n[0] * s.n[1] * s.n[3] * S * (4 + s.n[5]) : 0;
 }
 
 bool zg_launch_mix_op(const ZgOp& op, float* const* bufs, float* scratch, cudaStream_t st) {
@@ -412,8 +615,26 @@ bool zg_launch_mix_op(const ZgOp& op, float* const* bufs, float* scratch, cudaSt
             a.dst = bufs[s.buf[0]]; a.q = bufs[s.buf[1]]; a.kc = bufs[s.buf[2]]; a.vc = bufs[s.buf[3]]; a.ctl = bufs[s.buf[4]];
             a.T = s.n[0]; a.H = s.n[1]; a.G = s.n[2]; a.maps = s.n[3]; a.dk = s.n[4]; a.dv = s.n[5]; a.q_rs = s.n[6]; a.q_off = s.off[0];
             a.kw = s.n[7]; a.k_off = s.off[1]; a.vw = s.n[8]; a.v_off = s.off[2]; a.R = s.n[9]; a.kind = s.off[3]; a.size = s.off[4]; a.scale = s.f[0];
-            const uint32_t warps = 4, items = a.T * a.H * a.maps;
-            launch_pdl(k_cached_attention, dim3((items + warps - 1) / warps), dim3(warps * 32), warps * a.dk * sizeof(float), st, a);
+            const bool aligned = ca_aligned(s) && ((reinterpret_cast<uintptr_t>(a.q) | reinterpret_cast<uintptr_t>(a.kc) | reinterpret_cast<uintptr_t>(a.vc)) & 15) == 0;
+            if (aligned) {
+                const uint32_t S = scratch ? ca_splits(s) : 1;
+                float* part = S > 1 ? scratch : nullptr;
+                if (a.dv > 128) launch_cached_attention_tiled<16>(a, S, part, st);
+                else switch ((a.dv + 15) / 16) {
+                    case 1: launch_cached_attention_tiled<1>(a, S, part, st); break;
+                    case 2: launch_cached_attention_tiled<2>(a, S, part, st); break;
+                    case 3: case 4: launch_cached_attention_tiled<4>(a, S, part, st); break;
+                    case 5: case 6: launch_cached_attention_tiled<6>(a, S, part, st); break;
+                    default: launch_cached_attention_tiled<8>(a, S, part, st); break;
+                }
+                if (S > 1) {
+                    ZG_SEQ_CHECK();
+                    launch_pdl(k_cached_attention_merge, dim3(a.T * a.H * a.maps), dim3(128), 0, st, a.dst, (const float*)part, a.dv, S);
+                }
+            } else {
+                const uint32_t warps = 4, items = a.T * a.H * a.maps;
+                launch_pdl(k_cached_attention, dim3((items + warps - 1) / warps), dim3(warps * 32), warps * a.dk * sizeof(float), st, a);
+            }
             ZG_SEQ_CHECK();
             return true;
         }
