@@ -773,18 +773,19 @@ def main():
     ap.add_argument("--no-check", action="store_true", help="skip the 2-layer oracle comparison")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-extras", action="store_true")
-    ap.add_argument("--arch", default="", choices=["", "lududra"],
-                    help="side bench instead of the default workload: prefill / decode throughput of that design next to a LLaMA of equal layer sizes")
+    ap.add_argument("--arch", default="", choices=["", "lududra", "vemepel"],
+                    help="side bench instead of the default workload: prefill / decode throughput of that design next to the framework's closest "
+                         "model at equal layer sizes (lududra: a LLaMA; vemepel: Lududra)")
     ap.add_argument("--sizes", default="", help="--arch: comma-separated size names (default: all)")
     ap.add_argument("--prefill-tokens", type=int, default=1024, help="--arch: tokens of the timed prefill chunk")
     ap.add_argument("--context", type=int, default=1024, help="--arch: tokens in the sequence before the timed decode steps")
     args = ap.parse_args()
-    if args.arch == "lududra":
+    if args.arch:
         sys.path.insert(0, os.path.join(ROOT, "scripts"))
-        import bench_lududra
+        side = __import__("bench_" + args.arch)
         if args.steps == 50:
             args.steps = 10
-        return bench_lududra.run(args)
+        return side.run(args)
     if args.impl == "reference":
         run_reference(args)
     else:

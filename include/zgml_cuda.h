@@ -96,7 +96,10 @@ typedef enum ZgOpTag {
  *                   with buf 6 (single-row steps): the last output of the launch then passes a TOKEN_SHIFT (mix at off 2 of the
  *                   arena of the norm it follows, state buf 6, ctl buf 7) in the same launch
  *                   w and w2 must be constants of the model (an uploaded arena): they are read before the producing op of src has finished
- *                   buf 0 dst 1 src 2 w 3 res 4 dst2 5 w2 6 shift state 7 ctl | off 0 w 1 w2 2 shift mix 3 dst | n 0 rows 1 cols 2 kind 3 wdt
+ *                   with n 5 > 0 (no res, no chained norm): the row that is normed is the DEPTH_MIX of n5 streams of src (stride n6,
+ *                   coefficients at off 4 of w's arena); buf 4 receives that average itself
+ *                   buf 0 dst 1 src 2 w 3 res 4 dst2 5 w2 6 shift state 7 ctl | off 0 w 1 w2 2 shift mix 3 dst 4 average coefficients
+ *                   n 0 rows 1 cols 2 kind 3 wdt 5 averaged streams 6 their stride
  *                   4 kind of dst2 | f 0 eps 1 gain
  * WINDOW_ATTENTION  causal attention over the last `window` positions whose keys double as values (one projection, one cache),
  *                   grouped query heads, scores capped smoothly (cap * tanh(s / cap), f1 = 0: off), a per-distance per-head
@@ -161,9 +164,10 @@ typedef enum ZgOpTag {
  *                   buf 0 dst [rows, dv] 1 src [rows, 2, dv] | n 0 rows 1 dv | f 0 lambda 1 eps 2 output scale
  * GATE              dst[t, c] *= sigmoid(gate[t, c / group]), in place (group = dv: one gate per head; 1: per element)
  *                   buf 0 dst 1 gate | off 0 gate column | n 0 T 1 columns 2 group 3 gate row stride 4 dst row stride
- * HEAD_LINEAR       a block-diagonal product: dst[t, h, n] = sum_k src[t, h, k] W[h, n, k], W stacked [H, N, K]
- *                   buf 0 dst 1 src 2 W | off 0 W 1 src column 2 dst column | n 0 T 1 H 2 N 3 K 4 src head stride 5 src row
- *                   stride 6 dst head stride 7 dst row stride 8 wdt
+ * HEAD_LINEAR       a block-diagonal product: dst[t, h, n] = sum_k src[t, h, k] W[h, n, k], W stacked [H, N, K]; with buf 3 the
+ *                   result is multiplied by sigmoid(gate[t, (h N + n) / group]) (the GATE op in the epilogue)
+ *                   buf 0 dst 1 src 2 W 3 gate | off 0 W 1 src column 2 dst column 3 gate column 4 gate row stride
+ *                   n 0 T 1 H 2 N 3 K 4 src head stride 5 src row stride 6 dst head stride 7 dst row stride 8 wdt 9 gate group
  * POLY_NORM         dst[t] = a N(z) + b N(z^2) + c N(z^3) + e with N(v) = v / sqrt(mean(v^2) + f0) over the row, powers taken
  *                   element by element, (a, b, c, e) four weights; may run in place
  *                   buf 0 dst 1 src 2 coefficients | off 0 coefficients | n 0 T 1 columns 2 wdt | f 0 eps */

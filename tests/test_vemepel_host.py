@@ -75,8 +75,11 @@ def test_state_and_lowering_shape(fake_device):
         tags = [op.tag for op in lp.program.ops]
         assert tags[0] == abi.OP_EMBED and lp.logits_rows == rows and (lp.buf_logits is None) == (head == "none")
         assert tags.count(abi.OP_CACHED_ATTENTION) == 4 and tags.count(abi.OP_CACHE_APPEND) == 3 and tags.count(abi.OP_MAP_COMBINE) == 2
-        assert tags.count(abi.OP_HEAD_LINEAR) == 4 and tags.count(abi.OP_ROTARY) == 1 and tags.count(abi.OP_GATE) == 2
-        assert tags.count(abi.OP_DEPTH_MIX) == 4 and tags.count(abi.OP_POLY_NORM) == 1 and tags.count(abi.OP_MOE_FFN) == 2
+        assert tags.count(abi.OP_HEAD_LINEAR) == 4 and tags.count(abi.OP_ROTARY) == 1 and tags.count(abi.OP_GATE) == 0     # gates ride in the value products
+        # the depth average rides in the norm that opens the next layer (and in the head's norm): no launch of its own
+        averaged = [op for op in lp.program.ops if op.tag == abi.OP_NORM and op.u.seq.n[5]]
+        assert tags.count(abi.OP_DEPTH_MIX) == 0 and [op.u.seq.n[5] for op in averaged] == [2, 3, 4] + ([5] if head != "none" else [])
+        assert tags.count(abi.OP_POLY_NORM) == 1 and tags.count(abi.OP_MOE_FFN) == 2
         assert tags.count(abi.OP_TOKEN_SHIFT) == (0 if T == 1 else 4)     # single-token steps shift inside the opening norm
         ext = [e.buf_idx for e in lp.program.externs]
         assert len(set(ext)) == len(ext) == 5 + 7                           # weight arenas + state buffers, each once

@@ -217,14 +217,20 @@ class DeviceOp:
 
     @staticmethod
     def norm(dst, src, w, w_off, rows, cols, eps, wdt, kind="layer", res=None, then=None, then_w=None, then_w_off=0, then_kind="layer",
-             gain=None, shift_state=None, shift_off=0, ctl=None, dst_off=0):
+             gain=None, shift_state=None, shift_off=0, ctl=None, dst_off=0, average=None):
         """dst = (res +) norm(src; w); with `then`, also then = norm(dst; weights at then_w_off of arena then_w) in the same launch.
         Kinds: "layer", "rms", and "rms1" (RMS norm whose weight is stored around zero, applied as 1 + w).  `gain` multiplies the
         result(s); `shift_state` (single-row steps, with `then`) passes `then` through a token shift whose mix lies at shift_off of
-        then_w and whose carried row is that state buffer."""
+        then_w (of w without `then`) and whose carried row is that state buffer.  `average` = (out, coeff_off, terms, stride): the
+        row that is normed is sum_j coeff[j] * src[j * stride + .] (coefficients in w's arena), which also goes to buffer `out`."""
         kinds = {"layer": abi.NORM_LAYER, "rms": abi.NORM_RMS, "rms1": abi.NORM_RMS | abi.NORM_UNIT_OFFSET}
         g = abi.NORM_GAIN if gain is not None else 0       # the gain belongs to the last norm of the launch
         fused = shift_state is not None
+        if average is not None:
+            assert then is None and res is None
+            then, (avg_off, avg_terms, avg_stride) = average[0], average[1:]
+            return DeviceOp._seq(abi.OP_NORM, [dst, src, w, None, then, None, shift_state, ctl if fused else None], [w_off, 0, shift_off, dst_off, avg_off],
+                                 [rows, cols, kinds[kind] | g, wdt, 0, avg_terms, avg_stride], [eps, gain if gain is not None else 0.0])
         return DeviceOp._seq(abi.OP_NORM, [dst, src, w, res, then, then_w if then is not None else None, shift_state, ctl if fused else None],
                              [w_off, then_w_off, shift_off, dst_off],
                              [rows, cols, kinds[kind] | (g if then is None else 0), wdt, kinds[then_kind] | (g if then is not None else 0)],
@@ -294,9 +300,10 @@ class DeviceOp:
         return DeviceOp._seq(abi.OP_GATE, [dst, gate], [gate_col], [T, cols, group, gate_rs, dst_rs or cols])
 
     @staticmethod
-    def head_linear(dst, src, w, w_off, T, H, N, K, wdt, src_col=0, src_hs=0, src_rs=0, dst_col=0, dst_hs=0, dst_rs=0):
-        return DeviceOp._seq(abi.OP_HEAD_LINEAR, [dst, src, w], [w_off, src_col, dst_col],
-                             [T, H, N, K, src_hs or K, src_rs or H * K, dst_hs or N, dst_rs or H * N, wdt])
+    def head_linear(dst, src, w, w_off, T, H, N, K, wdt, src_col=0, src_hs=0, src_rs=0, dst_col=0, dst_hs=0, dst_rs=0, gate=None, gate_col=0, gate_rs=0,
+                    gate_group=1):
+        return DeviceOp._seq(abi.OP_HEAD_LINEAR, [dst, src, w, gate], [w_off, src_col, dst_col, gate_col, gate_rs],
+                             [T, H, N, K, src_hs or K, src_rs or H * K, dst_hs or N, dst_rs or H * N, wdt, gate_group if gate is not None else 0])
 
     @staticmethod
     def poly_norm(dst, src, w, coeff_off, T, cols, eps, wdt):

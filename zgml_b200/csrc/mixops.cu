@@ -170,9 +170,10 @@ __global__ void k_cached_attention(CaArgs a) {
 // masks reach: the scores accumulate over 64-wide slices of the key dimension (any dk), thread (ty, tx) of 16 x 16 holding
 // rows 4 ty .. 4 ty + 3 against keys tx + 16 c; the row statistics of the running softmax are shared through half-warp
 // shuffles, the probabilities pass through shared memory, value columns tx + 16 c accumulate in registers.  With `splits`
-// > 1 (few rows, long caches: decoding) the key tiles are dealt to gridDim.z CTAs, each leaving (max, sum, unnormalised
-// output) per row for k_cached_attention_merge.
-constexpr int kCtBQ = 64, kCtBK = 64, kCtDS = 64, kCtThreads = 256, kCtMaxSplits = 32;
+// > 1 (few rows, long caches: decoding) the keys are dealt in contiguous ranges to gridDim.z CTAs, each leaving (max, sum,
+// unnormalised output) per row for k_cached_attention_merge; a range may be shorter than a tile (its other keys are neither
+// loaded nor counted), since what bounds such a step is how many SMs pull on the cache, not the arithmetic.
+constexpr int kCtBQ = 64, kCtBK = 64, kCtDS = 64, kCtThreads = 256, kCtMaxSplits = 64, kCtMinShare = 32;
 template <int OC>
 __global__ void __launch_bounds__(kCtThreads) k_cached_attention_tiled(CaArgs a, uint32_t rh, uint32_t n_tiles, uint32_t splits, float* __restrict__ part) {
     pdl_enter();
@@ -190,8 +191,8 @@ __global__ void __launch_bounds__(kCtThreads) k_cached_attention_tiled(CaArgs a,
     const uint32_t total = a.T * rh, r0 = tile * kCtBQ, nq = min((uint32_t)kCtBQ, total - r0);
     const uint32_t p_min = pos0 + r0 / rh, p_max = pos0 + (r0 + nq - 1) / rh;
     const uint32_t k_lo = mask_low(p_min, a.kind, a.size);
-    const uint32_t n_kt = (p_max - k_lo) / kCtBK + 1, per = (n_kt + splits - 1) / splits;
-    const uint32_t kt_begin = blockIdx.z * per, kt_end = min(n_kt, kt_begin + per);
+    const uint32_t n_keys = p_max - k_lo + 1, per = (n_keys + splits - 1) / splits;
+    const uint32_t k_begin = k_lo + blockIdx.z * per, k_end = min(p_max + 1, k_begin + per);   // this CTA's keys [k_begin, k_end)
     const float* kbase = a.kc + (size_t)slot * a.R * a.kw + a.k_off + (size_t)gm * a.dk;
     const float* vbase = a.vc + (size_t)slot * a.R * a.vw + a.v_off + (size_t)g * a.dv + (size_t)vs * DV;
     const uint32_t v_cols = min((uint32_t)DV, a.dv - vs * DV);
@@ -222,8 +223,7 @@ __global__ void __launch_bounds__(kCtThreads) k_cached_attention_tiled(CaArgs a,
 #pragma unroll
         for (int c = 0; c < OC; c++) o[r][c] = 0.0f;
     }
-    for (uint32_t kt = kt_begin; kt < kt_end; kt++) {
-        const uint32_t s0 = k_lo + kt * kCtBK;
+    for (uint32_t s0 = k_begin; s0 < k_end; s0 += kCtBK) {
         float sc[4][4];
 #pragma unroll
         for (int r = 0; r < 4; r++)
@@ -235,14 +235,14 @@ __global__ void __launch_bounds__(kCtThreads) k_cached_attention_tiled(CaArgs a,
             for (uint32_t i = tid; i < kCtBK * (kCtDS / 4); i += kCtThreads) {
                 const uint32_t rr = i / (kCtDS / 4), c4 = i % (kCtDS / 4);
                 float4 val = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (s0 + rr <= p_max && d0 + 4 * c4 < a.dk) val = *reinterpret_cast<const float4*>(kbase + (size_t)((s0 + rr) % a.R) * a.kw + d0 + 4 * c4);
+                if (s0 + rr < k_end && d0 + 4 * c4 < a.dk) val = *reinterpret_cast<const float4*>(kbase + (size_t)((s0 + rr) % a.R) * a.kw + d0 + 4 * c4);
                 *reinterpret_cast<float4*>(Ks + rr * KP + 4 * c4) = val;
             }
             if (d0 == 0) {
                 for (uint32_t i = tid; i < kCtBK * (DV / 4); i += kCtThreads) {
                     const uint32_t rr = i / (DV / 4), c4 = i % (DV / 4);
                     float4 val = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (s0 + rr <= p_max && 4 * c4 < v_cols) val = *reinterpret_cast<const float4*>(vbase + (size_t)((s0 + rr) % a.R) * a.vw + 4 * c4);
+                    if (s0 + rr < k_end && 4 * c4 < v_cols) val = *reinterpret_cast<const float4*>(vbase + (size_t)((s0 + rr) % a.R) * a.vw + 4 * c4);
                     *reinterpret_cast<float4*>(Vs + rr * DV + 4 * c4) = val;
                 }
             }
@@ -271,7 +271,7 @@ __global__ void __launch_bounds__(kCtThreads) k_cached_attention_tiled(CaArgs a,
 #pragma unroll
             for (int c = 0; c < 4; c++) {
                 const uint32_t j = s0 + tx + 16 * c;
-                const float sv = (ok_r[r] && j <= p_r[r] && j >= lo_r[r]) ? sc[r][c] * a.scale : -INFINITY;
+                const float sv = (ok_r[r] && j <= p_r[r] && j >= lo_r[r] && j < k_end) ? sc[r][c] * a.scale : -INFINITY;
                 sc[r][c] = sv;
                 rmax = fmaxf(rmax, sv);
             }
@@ -325,19 +325,21 @@ __global__ void __launch_bounds__(kCtThreads) k_cached_attention_tiled(CaArgs a,
         }
     }
 }
-// merge of the key shares: one CTA per (token, head, map)
+// merge of the key shares: one CTA per (token, head, map); a share that saw no key carries max = -inf and weighs nothing
 __global__ void k_cached_attention_merge(float* __restrict__ dst, const float* __restrict__ part, uint32_t dv, uint32_t splits) {
     pdl_enter();
+    __shared__ float w[kCtMaxSplits];
     const float* P = part + (size_t)blockIdx.x * splits * (4 + dv);
     float M = -INFINITY;
     for (uint32_t i = 0; i < splits; i++) M = fmaxf(M, P[i * (4 + dv)]);
     float L = 0.0f;
     for (uint32_t i = 0; i < splits; i++) { const float mi = P[i * (4 + dv)]; if (mi != -INFINITY) L += P[i * (4 + dv) + 1] * expf(mi - M); }
-    const float inv = 1.0f / L;
+    if (threadIdx.x < splits) { const float mi = P[threadIdx.x * (4 + dv)]; w[threadIdx.x] = mi == -INFINITY ? 0.0f : expf(mi - M) / L; }
+    __syncthreads();
     for (uint32_t c = threadIdx.x; c < dv; c += blockDim.x) {
         float acc = 0.0f;
-        for (uint32_t i = 0; i < splits; i++) { const float mi = P[i * (4 + dv)]; if (mi != -INFINITY) acc = fmaf(P[i * (4 + dv) + 4 + c], expf(mi - M), acc); }
-        dst[(size_t)blockIdx.x * dv + c] = acc * inv;
+        for (uint32_t i = 0; i < splits; i++) if (w[i] != 0.0f) acc = fmaf(P[i * (4 + dv) + 4 + c], w[i], acc);
+        dst[(size_t)blockIdx.x * dv + c] = acc;
     }
 }
 template <int OC>
@@ -358,7 +360,7 @@ static uint32_t ca_splits(const ZgSeqOp& s) {
     const uint32_t rh = s.n[1] / s.n[2], n_tiles = (s.n[0] * rh + kCtBQ - 1) / kCtBQ, dvs = s.n[5] > 128 ? 256 : 128;
     const uint32_t ctas = n_tiles * s.n[2] * s.n[3] * ((s.n[5] + dvs - 1) / dvs);
     const uint32_t reach = s.off[3] ? min(s.n[9], s.off[4] + s.n[0]) : s.n[9];     // keys a row can see at most
-    uint32_t S = 296 / (ctas ? ctas : 1), most = reach / 128;
+    uint32_t S = 160 / (ctas ? ctas : 1), most = reach / kCtMinShare;
     if (S > most) S = most;
     return S < 2 ? 1 : (S > (uint32_t)kCtMaxSplits ? (uint32_t)kCtMaxSplits : S);
 }
@@ -388,9 +390,12 @@ __global__ void k_gate(float* __restrict__ dst, const float* __restrict__ gate, 
 
 // ── HEAD_LINEAR ──────────────────────────────────────────────────────────────────────────────────────────────────
 struct HlArgs {
-    float* dst; const float* src;
-    uint32_t T, H, N, K, src_hs, src_rs, dst_hs, dst_rs;
+    float* dst; const float* src; const float* gate;   // gate: output (h, n) of row m is multiplied by sigmoid(gate[m, (h N + n) / group])
+    uint32_t T, H, N, K, src_hs, src_rs, dst_hs, dst_rs, gate_rs, gate_group;
 };
+__device__ __forceinline__ float hl_gated(const HlArgs& a, float v, uint32_t m, uint32_t h, uint32_t n) {
+    return a.gate ? v * sigmoidf_(a.gate[(size_t)m * a.gate_rs + (h * a.N + n) / a.gate_group]) : v;
+}
 constexpr int kHlRows = 8;
 // few rows: one warp per (head, output), the weight row streamed once for all rows
 template <typename WT>
@@ -413,7 +418,7 @@ __global__ void k_head_linear_rows(HlArgs a, const WT* __restrict__ W) {
     for (int m = 0; m < kHlRows; m++) {
         if (m < (int)a.T) {
             const float s = warp_sum(acc[m]);
-            if (lane == 0) a.dst[(size_t)m * a.dst_rs + (size_t)h * a.dst_hs + n] = s;
+            if (lane == 0) a.dst[(size_t)m * a.dst_rs + (size_t)h * a.dst_hs + n] = hl_gated(a, s, m, h, n);
         }
     }
 }
@@ -455,7 +460,7 @@ __global__ void __launch_bounds__(256) k_head_linear_tile(HlArgs a, const WT* __
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             const uint32_t n = n0 + tx * 4 + j;
-            if (n < a.N) a.dst[(size_t)m * a.dst_rs + (size_t)h * a.dst_hs + n] = acc[i][j];
+            if (n < a.N) a.dst[(size_t)m * a.dst_rs + (size_t)h * a.dst_hs + n] = hl_gated(a, acc[i][j], m, h, n);
         }
     }
 }
@@ -558,6 +563,10 @@ bool zg_mix_op_valid(const ZgOp& op, const size_t* elems, size_t n_bufs, char* w
             if (!fits(0, 0, (T - 1) * drs + s.off[2] + (H - 1) * dhs + N) || !fits(1, 0, (T - 1) * srs + s.off[1] + (H - 1) * shs + K) || !wfits(2, s.n[8], s.off[0], H * N * K))
                 return fail("head_linear: extent");
             if (s.buf[0] == s.buf[1]) return fail("head_linear: in place");
+            if (s.buf[3] != ZG_NO_BUF) {
+                const size_t group = s.n[9], grs = s.off[4];
+                if (!group || (H * N) % group || s.off[3] + H * N / group > grs || !fits(3, 0, (T - 1) * grs + s.off[3] + H * N / group) || s.buf[3] == s.buf[0]) return fail("head_linear: gate");
+            }
             return true;
         }
         case ZG_OP_POLY_NORM: {
@@ -652,6 +661,7 @@ bool zg_launch_mix_op(const ZgOp& op, float* const* bufs, float* scratch, cudaSt
             HlArgs a;
             a.dst = bufs[s.buf[0]] + s.off[2]; a.src = bufs[s.buf[1]] + s.off[1];
             a.T = s.n[0]; a.H = s.n[1]; a.N = s.n[2]; a.K = s.n[3]; a.src_hs = s.n[4]; a.src_rs = s.n[5]; a.dst_hs = s.n[6]; a.dst_rs = s.n[7];
+            a.gate = s.buf[3] != ZG_NO_BUF ? bufs[s.buf[3]] + s.off[3] : nullptr; a.gate_rs = s.off[4]; a.gate_group = s.n[9];
             ZG_SEQ_WDT(s.n[8], {
                 const WT* W = wptr<WT>(bufs, s.buf[2], s.off[0]);
                 if (a.T <= (uint32_t)kHlRows) launch_pdl(k_head_linear_rows<WT>, dim3((a.N + 7) / 8, a.H), dim3(256), 0, st, a, W);

@@ -219,7 +219,8 @@ __device__ __forceinline__ float norm_weight(float w, uint32_t kind, float gain)
 template <typename WT>
 __global__ void k_norm(float* __restrict__ dst, const float* __restrict__ src, const WT* __restrict__ w, const float* __restrict__ res,
                        uint32_t cols, uint32_t kind, float eps, float* __restrict__ dst2, const WT* __restrict__ w2, uint32_t kind2, float gain,
-                       const WT* __restrict__ shift_mix, float* __restrict__ shift_state, const float* __restrict__ ctl) {
+                       const WT* __restrict__ shift_mix, float* __restrict__ shift_state, const float* __restrict__ ctl,
+                       const WT* __restrict__ avg_coeff, uint32_t avg_terms, uint32_t avg_stride, float* __restrict__ avg_out) {
     // Rows that fit the registers: the norm weights are constants of the model and are read BEFORE the wait on the predecessor;
     // the row and the residual are read together right after it, so the kernel has one round of global loads, not three.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -241,12 +242,26 @@ __global__ void k_norm(float* __restrict__ dst, const float* __restrict__ src, c
 #pragma unroll
         for (int i = 0; i < kNormCache; i++) {
             const uint32_t c = threadIdx.x + i * blockDim.x;
-            v[i] = c < cols ? x[c] : 0.0f;
+            if (avg_terms && c < cols) {   // the row to norm is a weighted sum of `avg_terms` streams (a depth average), kept in avg_out too
+                float acc = 0.0f;
+                for (uint32_t j = 0; j < avg_terms; j++) acc = fmaf(wld(avg_coeff, j), x[(size_t)j * avg_stride + c], acc);
+                v[i] = acc;
+                avg_out[row + c] = acc;
+            } else v[i] = c < cols ? x[c] : 0.0f;
             rv[i] = (res && c < cols) ? res[row + c] : 0.0f;
         }
         norm_pass<true>(dst + row, x, v, res ? res + row : nullptr, rv, cols, kind, eps, sh, dst2 != nullptr, [&](int i, uint32_t) { return wa[i]; });
         if (dst2) norm_pass<true>(dst2 + row, dst + row, v, nullptr, rv, cols, kind2, eps, sh, false, [&](int i, uint32_t) { return wb[i]; });
     } else {
+        if (avg_terms) {
+            for (uint32_t c = threadIdx.x; c < cols; c += blockDim.x) {
+                float acc = 0.0f;
+                for (uint32_t j = 0; j < avg_terms; j++) acc = fmaf(wld(avg_coeff, j), x[(size_t)j * avg_stride + c], acc);
+                avg_out[row + c] = acc;
+            }
+            __syncthreads();
+            x = avg_out + row;
+        }
         norm_pass<false>(dst + row, x, v, res ? res + row : nullptr, rv, cols, kind, eps, sh, false, [&](int, uint32_t c) { return norm_weight(wld(w, c), kind, gain); });
         if (dst2) {
             __syncthreads();                           // the row just written is read back by other threads
@@ -1233,6 +1248,13 @@ bool zg_seq_op_valid(const ZgOp& op, const size_t* elems, size_t n_bufs, char* w
             const size_t n = (size_t)s.n[0] * s.n[1];
             if (!n || s.n[2] > 7) return fail("norm: shape");
             if (!fits(0, s.off[3], n) || !fits(1, 0, n) || !wfits(2, s.off[0], s.n[1])) return fail("norm: extent");
+            if (s.n[5]) {      // averaged source
+                if (s.n[6] < n || !fits(1, 0, (size_t)(s.n[5] - 1) * s.n[6] + n) || !wfits(2, s.off[4], s.n[5]) || s.buf[3] != ZG_NO_BUF || !fits(4, 0, n) || s.buf[4] == s.buf[0] ||
+                    s.buf[4] == s.buf[1])
+                    return fail("norm: averaged source");
+                if (s.buf[6] != ZG_NO_BUF && (s.n[0] != 1 || !have(6) || elems[s.buf[6]] < s.n[1] || !wfits(2, s.off[2], s.n[1]) || !fits(7, 0, ZG_CTL_IDS))) return fail("norm: fused token shift (single-row steps)");
+                return true;
+            }
             if (s.buf[3] != ZG_NO_BUF && !fits(3, 0, n)) return fail("norm: residual extent");
             if (s.buf[4] != ZG_NO_BUF && (s.n[4] > 7 || !fits(4, 0, n) || !wfits(5, s.off[1], s.n[1]) || s.buf[4] == s.buf[0] || s.buf[4] == s.buf[1] || s.buf[4] == s.buf[3]))
                 return fail("norm: chained norm");
@@ -1364,9 +1386,12 @@ bool zg_launch_seq_op(ZgCudaCtx* ctx, const ZgOp& op, float* const* bufs, float*
             const float* res = s.buf[3] != ZG_NO_BUF ? bufs[s.buf[3]] : nullptr;
             float* dst2 = s.buf[4] != ZG_NO_BUF ? bufs[s.buf[4]] : nullptr;
             float* shift_state = s.buf[6] != ZG_NO_BUF ? bufs[s.buf[6]] : nullptr;
+            const uint32_t avg_terms = s.n[5];             // averaged source: buf 4 receives the average instead of a chained norm
+            if (avg_terms) dst2 = nullptr;
             ZG_SEQ_WDT(s.n[3], launch_pdl(k_norm<WT>, dim3(s.n[0]), dim3(256), 0, st, bufs[s.buf[0]] + s.off[3], bufs[s.buf[1]], wptr<WT>(bufs, s.buf[2], s.off[0]), res, s.n[1], s.n[2], s.f[0],
                                           dst2, dst2 ? wptr<WT>(bufs, s.buf[5], s.off[1]) : nullptr, s.n[4], s.f[1],
-                                          shift_state ? wptr<WT>(bufs, s.buf[dst2 ? 5 : 2], s.off[2]) : nullptr, shift_state, shift_state ? bufs[s.buf[7]] : nullptr));
+                                          shift_state ? wptr<WT>(bufs, s.buf[dst2 ? 5 : 2], s.off[2]) : nullptr, shift_state, shift_state ? bufs[s.buf[7]] : nullptr,
+                                          avg_terms ? wptr<WT>(bufs, s.buf[2], s.off[4]) : nullptr, avg_terms, s.n[6], avg_terms ? bufs[s.buf[4]] : nullptr));
             ZG_SEQ_CHECK();
             return true;
         }

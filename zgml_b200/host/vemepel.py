@@ -20,7 +20,8 @@ latent attention   [q | dkv | gate] = W h in ONE matmul; CACHE_APPEND norms the 
                    on its way into the cache.  Attention runs in the ABSORBED form: per head q' = W_uk^T q (HEAD_LINEAR
                    over the transposed up-projection), scores and the weighted sum are taken against the cached latent
                    itself (one key / value head of kv_rank (+ rot_dim) columns serving all heads), and the value
-                   up-projection is applied to the result (HEAD_LINEAR), so nothing per head is ever cached or re-expanded.
+                   up-projection is applied to the result (HEAD_LINEAR, the sigmoid gate in its epilogue), so nothing per head
+                   is ever cached or re-expanded.
 feed-forward       dense: W_up, POLY_NORM, W_down.  moe: router matmul, ROUTE (bias added, top-k, softmax over the chosen),
                    MOE_FFN over stacked expert weights.
 """
@@ -124,7 +125,8 @@ class VemepelModel:
                 A.add(n, t)
             dwa = tensors(p + "dwa")
             assert dwa.shape == (i + 2,), f"{p}dwa: shape {dwa.shape}"
-            A.add("dwa", dwa)
+            if i:      # the average that ENTERS this layer is taken by its opening norm: the previous layer's coefficients live here
+                A.add("avg_in", tensors(f"l{i - 1}.dwa"))
             H, dim, vdim = m["heads"], m["dim"], m["vdim"]
             if L["type"] == "attention":
                 G = m["kv_heads"]
@@ -187,6 +189,7 @@ class VemepelModel:
         assert emb.shape == (cfg.vocab, D) and head.shape == (cfg.vocab, D)
         A.add("embed", emb)
         A.add("final.norm", tensors("final.norm"))
+        A.add("avg_in", tensors(f"l{len(cfg.layers) - 1}.dwa"))
         A.add("head", head)
         self.arenas.append(A)
         self.buffers.append(A.upload(be))
@@ -277,10 +280,18 @@ class VemepelModel:
             H, dim, vdim = m["heads"], m["dim"], m["vdim"]
             ni = meta["n_in"]
             shift_state = ext(pool.buffers[f"l{i}.shift"])
-            if T == 1:   # single-token steps: the opening norm shifts its own row against the carried one, in the same launch
-                ops.append(DeviceOp.norm(h, x, wb, A.off["norm1"], T, D, eps, wdt, kind="rms1", shift_state=shift_state, shift_off=A.off["shift"], ctl=ctl))
+            # The opening norm also takes the depth average that enters the layer (layer 0 reads the embedding itself) and, in
+            # single-token steps, shifts its own row against the carried one: one launch.
+            average = None
+            if i:
+                x = new(TD) if keep_layers else xm
+                average = (x, A.off["avg_in"], i + 1, TD)
+                layer_bufs.append(x)
+            src = hist
+            if T == 1:
+                ops.append(DeviceOp.norm(h, src, wb, A.off["norm1"], T, D, eps, wdt, kind="rms1", shift_state=shift_state, shift_off=A.off["shift"], ctl=ctl, average=average))
             else:
-                ops.append(DeviceOp.norm(h0, x, wb, A.off["norm1"], T, D, eps, wdt, kind="rms1"))
+                ops.append(DeviceOp.norm(h0, src, wb, A.off["norm1"], T, D, eps, wdt, kind="rms1", average=average))
                 ops.append(DeviceOp.token_shift(h, h0, wb, A.off["shift"], shift_state, ctl, T, D, wdt))
             ops.append(DeviceOp.linear(proj, h, wb, A.off["in"], T, ni, D, wdt))
             if L["type"] == "attention":
@@ -307,8 +318,9 @@ class VemepelModel:
                     ops.append(DeviceOp.rotary(qa, ctl, rank, T, H, cw, H * cw, rd, m["rot"]["base"], src=proj, src_col=dim, src_hs=dim + rd, src_rs=ni))
                 lat = scratch("latent_out", T * H * rank)
                 ops.append(DeviceOp.cached_attention(lat, qa, ext(cache), ext(cache), ctl, 0, 0, 0, T, H, 1, 1, cw, rank, H * cw, cw, cw, R, m["scale"]))
-                ops.append(DeviceOp.head_linear(mix, lat, wb, A.off["uv"], T, H, vdim, rank, wdt))
-                ops.append(DeviceOp.gate(mix, proj, meta["g_off"], T, H * vdim, vdim if meta["ng"] == H else 1, ni))
+                # the value up-projection, with the output gate (one per head, or one per element) in its epilogue
+                ops.append(DeviceOp.head_linear(mix, lat, wb, A.off["uv"], T, H, vdim, rank, wdt, gate=proj, gate_col=meta["g_off"], gate_rs=ni,
+                                                gate_group=vdim if meta["ng"] == H else 1))
             ops.append(DeviceOp.linear(y, mix, wb, A.off["o"], T, D, H * vdim, wdt))
             mlp = L["mlp"]
             out_off = (i + 1) * TD
@@ -334,15 +346,16 @@ class VemepelModel:
                     moe_op.u.seq.buf[4] = scratch("expert", seq_scratch_elems(moe_op))   # the library knows what its kernels stage
                     ops.append(moe_op)
                 ops.append(DeviceOp.norm(hist, y, wb, A.off["norm2b"], T, D, eps, wdt, kind="rms1", res=xa, dst_off=out_off))
-            x = new(TD) if keep_layers else xm      # the stream that entered this layer is not read again
-            ops.append(DeviceOp.depth_mix(x, hist, wb, A.off["dwa"], TD, i + 2, TD, wdt))
-            layer_bufs.append(x)
         logits, rows = None, 0
+        x = new(TD) if keep_layers else xm          # the average over all layers: what the head reads
+        layer_bufs.append(x)
         if head != "none":
-            ops.append(DeviceOp.norm(h, x, gl, GA.off["final.norm"], T, D, eps, wdt, kind="rms1", gain=cfg.logit_scale))
+            ops.append(DeviceOp.norm(h, hist, gl, GA.off["final.norm"], T, D, eps, wdt, kind="rms1", gain=cfg.logit_scale, average=(x, GA.off["avg_in"], nL + 1, TD)))
             rows = T if head == "all" else 1
             logits = new(rows * cfg.vocab)
             ops.append(DeviceOp.linear(logits, h, gl, GA.off["head"], rows, cfg.vocab, D, wdt, src_off=0 if head == "all" else (T - 1) * D))
+        elif keep_layers:
+            ops.append(DeviceOp.depth_mix(x, hist, gl, GA.off["avg_in"], TD, nL + 1, TD, wdt))
         prog = DeviceProgram(ops, sizes, uploads, [], externs)
         return LoweredProgram(prog, ctl, logits, rows, layer_bufs if keep_layers else None)
 
@@ -350,3 +363,86 @@ class VemepelModel:
         for b in self.buffers:
             b.free()
         self.buffers = []
+
+
+def synthetic_config(width: int, n_layers: int, heads: int, kv_heads: int, dim: int, block: int, experts: int, top: int, ff: int, vocab: int,
+                     kv_rank: int = 512, rot_dim: int = 64) -> dict:
+    """config.json contents of a random-init model: the layers cycle through differential attention (grouped heads, two maps of
+    dim / 2 each, every second one borrowing the keys and values of the one before), latent attention with a rotated key
+    part and latent attention without; feed-forwards alternate between routed experts and a dense PolyNorm layer as wide as
+    the experts a token uses."""
+    layers, last_owner = [], None
+    for i in range(n_layers):
+        mlp = ({"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top}} if i % 2 == 0 else {"kind": "dense", "ff": top * ff})
+        kind = i % 3
+        if kind == 0:
+            mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim // 2, "vdim": dim, "mask": {"size": block}, "diff": 0.5, "scale": (dim // 2) ** -0.5}
+            if last_owner is not None:
+                mixer["kv_from"], last_owner = last_owner, None
+            else:
+                last_owner = i
+            layers.append({"type": "attention", "mixer": mixer, "mlp": mlp})
+        elif kind == 1:
+            mixer = {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": dim, "kv_rank": kv_rank, "rot": {"base": 10000.0, "dims": rot_dim},
+                     "scale": (dim + rot_dim) ** -0.5}
+            layers.append({"type": "latent_attention_2", "mixer": mixer, "mlp": mlp})
+        else:
+            layers.append({"type": "latent_attention", "mixer": {"heads": heads, "dim": dim, "vdim": dim, "kv_rank": kv_rank, "scale": dim ** -0.5}, "mlp": mlp})
+    return {"architecture": ARCHITECTURE, "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "logit_scale": 1.0, "layers": layers}
+
+
+def synthetic_tensors(cfg: dict, seed: int = 0):
+    """Accessor name -> random f32 tensor of the shape the configuration implies (benchmarks and smoke runs; values are
+    scaled like a trained model's so that activations stay O(1))."""
+    D = cfg["width"]
+
+    def shape_of(name):
+        if name in ("embed", "head"):
+            return (cfg["vocab"], D)
+        if name == "final.norm":
+            return (D,)
+        layer, rest = name.split(".", 1)
+        i = int(layer[1:])
+        L = cfg["layers"][i]
+        m = L["mixer"]
+        H, d, dv = m["heads"], m["dim"], m["vdim"]
+        if rest.startswith("norm") or rest == "shift":
+            return (D,)
+        if rest == "dwa":
+            return (i + 2,)
+        if rest.startswith("mlp."):
+            part = rest.split(".", 1)[1]
+            if L["mlp"]["kind"] == "dense":
+                return {"up": (L["mlp"]["ff"], D), "down": (D, L["mlp"]["ff"]), "act": (4,)}[part]
+            E, ff = L["mlp"]["router"]["experts"], L["mlp"]["expert"]["ff"]
+            return {"router": (E, D), "router.b": (E,), "gate": (ff, D), "up": (ff, D), "down": (D, ff)}[part.split(".")[-1] if part.startswith("e") else part]
+        t = rest[len("mix."):]
+        if L["type"] == "attention":
+            G = m["kv_heads"]
+            return {"q": (H * 2 * d, D), "k": (G * 2 * d, D), "v": (G * dv, D), "lq1": (d,), "lk1": (d,), "lq2": (d,), "lk2": (d,), "o": (D, H * dv)}[t]
+        rd, rank = m.get("rot_dim", 0), m["kv_rank"]
+        return {"q": (H * (d + rd), D), "dkv": (rank + rd, D), "dkv.norm": (rank,), "uk": (H * d, rank), "uv": (H * dv, rank),
+                "g": (H * dv if L["type"] == "latent_attention_2" else H, D), "o": (D, H * dv)}[t]
+
+    def get(name):
+        import zlib
+        shp = shape_of(name)
+        r = np.random.default_rng([seed, zlib.crc32(name.encode())])
+        if name.endswith("dkv.norm"):
+            return np.ones(shp, np.float32)
+        if name.endswith(".dwa"):
+            a = np.full(shp, 0.1 / shp[0], np.float32)
+            a[-1] = 1.0
+            return a
+        if name.endswith(".act"):
+            return np.array([0.6, 0.3, 0.1, 0.0], np.float32)
+        if name.endswith(".shift"):
+            return r.random(shp, dtype=np.float32)
+        if len(shp) == 1:
+            return (r.random(shp, dtype=np.float32) - 0.5) * 0.2
+        a = r.random(shp, dtype=np.float32)
+        a -= 0.5
+        a *= np.float32(np.sqrt(12.0 / shp[1]))
+        return a
+
+    return get
