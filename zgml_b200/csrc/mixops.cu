@@ -325,22 +325,28 @@ __global__ void __launch_bounds__(kCtThreads) k_cached_attention_tiled(CaArgs a,
         }
     }
 }
-// merge of the key shares: one CTA per (token, head, map); a share that saw no key carries max = -inf and weighs nothing
-__global__ void k_cached_attention_merge(float* __restrict__ dst, const float* __restrict__ part, uint32_t dv, uint32_t splits) {
+// merge of the key shares: CTA (x, y) = 128 value columns y of (token, head, map) x; a share that saw no key carries
+// max = -inf and weighs nothing (its output is zero)
+__global__ void __launch_bounds__(128) k_cached_attention_merge(float* __restrict__ dst, const float* __restrict__ part, uint32_t dv, uint32_t splits) {
     pdl_enter();
     __shared__ float w[kCtMaxSplits];
     const float* P = part + (size_t)blockIdx.x * splits * (4 + dv);
-    float M = -INFINITY;
-    for (uint32_t i = 0; i < splits; i++) M = fmaxf(M, P[i * (4 + dv)]);
-    float L = 0.0f;
-    for (uint32_t i = 0; i < splits; i++) { const float mi = P[i * (4 + dv)]; if (mi != -INFINITY) L += P[i * (4 + dv) + 1] * expf(mi - M); }
-    if (threadIdx.x < splits) { const float mi = P[threadIdx.x * (4 + dv)]; w[threadIdx.x] = mi == -INFINITY ? 0.0f : expf(mi - M) / L; }
-    __syncthreads();
-    for (uint32_t c = threadIdx.x; c < dv; c += blockDim.x) {
-        float acc = 0.0f;
-        for (uint32_t i = 0; i < splits; i++) if (w[i] != 0.0f) acc = fmaf(P[i * (4 + dv) + 4 + c], w[i], acc);
-        dst[(size_t)blockIdx.x * dv + c] = acc;
+    if (threadIdx.x < 32) {                            // warp 0: the shares' weights exp(m_i - M) / L
+        float m0 = threadIdx.x < splits ? P[threadIdx.x * (4 + dv)] : -INFINITY, m1 = threadIdx.x + 32 < splits ? P[(threadIdx.x + 32) * (4 + dv)] : -INFINITY;
+        float l0 = threadIdx.x < splits ? P[threadIdx.x * (4 + dv) + 1] : 0.0f, l1 = threadIdx.x + 32 < splits ? P[(threadIdx.x + 32) * (4 + dv) + 1] : 0.0f;
+        const float M = warp_max(fmaxf(m0, m1));
+        const float e0 = m0 == -INFINITY ? 0.0f : expf(m0 - M), e1 = m1 == -INFINITY ? 0.0f : expf(m1 - M);
+        const float inv = 1.0f / warp_sum(l0 * e0 + l1 * e1);
+        if (threadIdx.x < splits) w[threadIdx.x] = e0 * inv;
+        if (threadIdx.x + 32 < splits) w[threadIdx.x + 32] = e1 * inv;
     }
+    __syncthreads();
+    const uint32_t c = blockIdx.y * 128 + threadIdx.x;
+    if (c >= dv) return;
+    float acc = 0.0f;
+#pragma unroll 4
+    for (uint32_t i = 0; i < splits; i++) acc = fmaf(P[i * (4 + dv) + 4 + c], w[i], acc);
+    dst[(size_t)blockIdx.x * dv + c] = acc;
 }
 template <int OC>
 static void launch_cached_attention_tiled(const CaArgs& a, uint32_t splits, float* part, cudaStream_t st) {
@@ -638,7 +644,7 @@ bool zg_launch_mix_op(const ZgOp& op, float* const* bufs, float* scratch, cudaSt
                 }
                 if (S > 1) {
                     ZG_SEQ_CHECK();
-                    launch_pdl(k_cached_attention_merge, dim3(a.T * a.H * a.maps), dim3(128), 0, st, a.dst, (const float*)part, a.dv, S);
+                    launch_pdl(k_cached_attention_merge, dim3(a.T * a.H * a.maps, (a.dv + 127) / 128), dim3(128), 0, st, a.dst, (const float*)part, a.dv, S);
                 }
             } else {
                 const uint32_t warps = 4, items = a.T * a.H * a.maps;

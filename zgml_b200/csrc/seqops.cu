@@ -239,16 +239,30 @@ __global__ void k_norm(float* __restrict__ dst, const float* __restrict__ src, c
     }
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (cached) {
+        if (avg_terms) {   // the row to norm is a weighted sum of `avg_terms` streams (a depth average), kept in avg_out too
 #pragma unroll
-        for (int i = 0; i < kNormCache; i++) {
-            const uint32_t c = threadIdx.x + i * blockDim.x;
-            if (avg_terms && c < cols) {   // the row to norm is a weighted sum of `avg_terms` streams (a depth average), kept in avg_out too
-                float acc = 0.0f;
-                for (uint32_t j = 0; j < avg_terms; j++) acc = fmaf(wld(avg_coeff, j), x[(size_t)j * avg_stride + c], acc);
-                v[i] = acc;
-                avg_out[row + c] = acc;
-            } else v[i] = c < cols ? x[c] : 0.0f;
-            rv[i] = (res && c < cols) ? res[row + c] : 0.0f;
+            for (int i = 0; i < kNormCache; i++) { v[i] = 0.0f; rv[i] = 0.0f; }
+            for (uint32_t j = 0; j < avg_terms; j++) {     // one batch of independent loads per stream
+                const float cj = wld(avg_coeff, j);
+                const float* xj = x + (size_t)j * avg_stride;
+#pragma unroll
+                for (int i = 0; i < kNormCache; i++) {
+                    const uint32_t c = threadIdx.x + i * blockDim.x;
+                    if (c < cols) v[i] = fmaf(cj, xj[c], v[i]);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < kNormCache; i++) {
+                const uint32_t c = threadIdx.x + i * blockDim.x;
+                if (c < cols) avg_out[row + c] = v[i];
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < kNormCache; i++) {
+                const uint32_t c = threadIdx.x + i * blockDim.x;
+                v[i] = c < cols ? x[c] : 0.0f;
+                rv[i] = (res && c < cols) ? res[row + c] : 0.0f;
+            }
         }
         norm_pass<true>(dst + row, x, v, res ? res + row : nullptr, rv, cols, kind, eps, sh, dst2 != nullptr, [&](int i, uint32_t) { return wa[i]; });
         if (dst2) norm_pass<true>(dst2 + row, dst + row, v, nullptr, rv, cols, kind2, eps, sh, false, [&](int i, uint32_t) { return wb[i]; });
