@@ -348,6 +348,139 @@ __global__ void __launch_bounds__(128) k_cached_attention_merge(float* __restric
     for (uint32_t i = 0; i < splits; i++) acc = fmaf(P[i * (4 + dv) + 4 + c], w[i], acc);
     dst[(size_t)blockIdx.x * dv + c] = acc;
 }
+
+// Few query rows (decoding: tokens x heads of a key group <= 16): what bounds the step is the latency of pulling the cache,
+// so a CTA takes one share of the keys, 32 at a time with WHOLE rows in shared memory — one round of loads per 32 keys instead
+// of one per 64-wide slice — and the shares are merged afterwards.  Thread (row, kq) of 16 x 16 scores keys kq and kq + 16
+// of its row; the 16 threads of a row keep the row's running (max, sum) in step through half-warp shuffles; for the weighted
+// sum thread t owns value columns t + 256 i of all rows.  Where the value row is the head of the key row itself (a latent that
+// serves as both), it is not loaded twice.
+constexpr int kCfRows = 16, kCfKeys = 32, kCfThreads = 256;
+template <int CI>
+__global__ void __launch_bounds__(kCfThreads) k_cached_attention_few(CaArgs a, uint32_t rh, uint32_t splits, float* __restrict__ part, uint32_t alias) {
+    pdl_enter();
+    extern __shared__ __align__(16) float sm[];
+    const uint32_t KP = a.dk + 4, VP = alias ? KP : a.dv;
+    float* Qs = sm;                                    // [16][dk]
+    float* Ks = Qs + kCfRows * a.dk;                   // [32][dk + 4]
+    float* Ss = Ks + kCfKeys * KP;                     // [16][32] scores, then probabilities
+    float* Al = Ss + kCfRows * kCfKeys;                // [16] rescale of the running sums (at the end: 1 / sum)
+    float* Vs = alias ? Ks : Al + kCfRows;             // [32][dv]
+    const uint32_t tid = threadIdx.x, row = tid >> 4, kq = tid & 15;
+    const uint32_t gm = blockIdx.x, g = gm / a.maps, m = gm % a.maps;
+    const uint32_t pos0 = (uint32_t)ctl_word(a.ctl, ZG_CTL_POS), slot = (uint32_t)ctl_word(a.ctl, ZG_CTL_SLOT);
+    const uint32_t total = a.T * rh, p_max = pos0 + a.T - 1;
+    const uint32_t k_lo = mask_low(pos0, a.kind, a.size);
+    const uint32_t n_keys = p_max - k_lo + 1, per = (n_keys + splits - 1) / splits;
+    const uint32_t k_begin = k_lo + blockIdx.y * per, k_end = min(p_max + 1, k_begin + per);
+    const float* kbase = a.kc + (size_t)slot * a.R * a.kw + a.k_off + (size_t)gm * a.dk;
+    const float* vbase = a.vc + (size_t)slot * a.R * a.vw + a.v_off + (size_t)g * a.dv;
+    const bool ok = row < total;
+    const uint32_t p_r = pos0 + (ok ? row / rh : 0), lo_r = mask_low(p_r, a.kind, a.size);
+    const uint32_t dk4 = a.dk / 4, dv4 = a.dv / 4;
+    for (uint32_t i = tid; i < total * dk4; i += kCfThreads) {
+        const uint32_t r = i / dk4, c4 = i % dk4;
+        *reinterpret_cast<float4*>(Qs + r * a.dk + 4 * c4) =
+            *reinterpret_cast<const float4*>(a.q + (size_t)(r / rh) * a.q_rs + a.q_off + (size_t)((g * rh + r % rh) * a.maps + m) * a.dk + 4 * c4);
+    }
+    float acc[kCfRows][CI];
+#pragma unroll
+    for (int r = 0; r < kCfRows; r++)
+#pragma unroll
+        for (int i = 0; i < CI; i++) acc[r][i] = 0.0f;
+    float m_run = -INFINITY, l_run = 0.0f;
+    for (uint32_t s0 = k_begin; s0 < k_end; s0 += kCfKeys) {
+        const uint32_t nk = min((uint32_t)kCfKeys, k_end - s0);
+        __syncthreads();                               // the previous keys' readers are done
+        for (uint32_t i = tid; i < nk * dk4; i += kCfThreads) {
+            const uint32_t kk = i / dk4, c4 = i % dk4;
+            *reinterpret_cast<float4*>(Ks + kk * KP + 4 * c4) = *reinterpret_cast<const float4*>(kbase + (size_t)((s0 + kk) % a.R) * a.kw + 4 * c4);
+        }
+        if (!alias)
+            for (uint32_t i = tid; i < nk * dv4; i += kCfThreads) {
+                const uint32_t kk = i / dv4, c4 = i % dv4;
+                *reinterpret_cast<float4*>(Vs + kk * VP + 4 * c4) = *reinterpret_cast<const float4*>(vbase + (size_t)((s0 + kk) % a.R) * a.vw + 4 * c4);
+            }
+        __syncthreads();
+        float sv[2];
+#pragma unroll
+        for (int u = 0; u < 2; u++) {
+            const uint32_t kk = kq + 16 * u, j = s0 + kk;
+            sv[u] = -INFINITY;
+            if (ok && kk < nk && j <= p_r && j >= lo_r) {
+                const float* qr = Qs + row * a.dk;
+                const float* kr = Ks + kk * KP;
+                float d0 = 0.0f, d1 = 0.0f;
+                for (uint32_t d = 0; d < a.dk; d += 4) {
+                    const float4 qv = *reinterpret_cast<const float4*>(qr + d), kv = *reinterpret_cast<const float4*>(kr + d);
+                    d0 = fmaf(qv.x, kv.x, fmaf(qv.y, kv.y, d0));
+                    d1 = fmaf(qv.z, kv.z, fmaf(qv.w, kv.w, d1));
+                }
+                sv[u] = (d0 + d1) * a.scale;
+            }
+        }
+        float rmax = fmaxf(sv[0], sv[1]);
+#pragma unroll
+        for (int off = 8; off > 0; off >>= 1) rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, off));
+        const float new_m = fmaxf(m_run, rmax);
+        const float alpha = m_run == -INFINITY ? (new_m == -INFINITY ? 1.0f : 0.0f) : expf(m_run - new_m);
+        float rsum = 0.0f;
+#pragma unroll
+        for (int u = 0; u < 2; u++) {
+            const float pv = sv[u] == -INFINITY ? 0.0f : expf(sv[u] - new_m);
+            Ss[row * kCfKeys + kq + 16 * u] = pv;
+            rsum += pv;
+        }
+#pragma unroll
+        for (int off = 8; off > 0; off >>= 1) rsum += __shfl_xor_sync(0xffffffffu, rsum, off);
+        l_run = l_run * alpha + rsum;
+        m_run = new_m;
+        if (kq == 0) Al[row] = alpha;
+        __syncthreads();
+#pragma unroll
+        for (int r = 0; r < kCfRows; r++) {
+            const float al = Al[r];
+#pragma unroll
+            for (int i = 0; i < CI; i++) acc[r][i] *= al;
+        }
+        for (uint32_t kk = 0; kk < nk; kk++) {
+            float v[CI];
+#pragma unroll
+            for (int i = 0; i < CI; i++) { const uint32_t c = tid + kCfThreads * i; v[i] = c < a.dv ? Vs[kk * VP + c] : 0.0f; }
+#pragma unroll
+            for (int r = 0; r < kCfRows; r++) {
+                const float pr = Ss[r * kCfKeys + kk];
+#pragma unroll
+                for (int i = 0; i < CI; i++) acc[r][i] = fmaf(pr, v[i], acc[r][i]);
+            }
+        }
+    }
+    __syncthreads();
+    if (kq == 0) Al[row] = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+    if (splits > 1 && kq == 0 && ok) {
+        float* mine = part + (((size_t)(row / rh) * a.H * a.maps + (g * rh + row % rh) * a.maps + m) * splits + blockIdx.y) * (4 + a.dv);
+        mine[0] = m_run; mine[1] = l_run;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < kCfRows; r++) {
+        if ((uint32_t)r >= total) break;
+        const size_t item = (size_t)((uint32_t)r / rh) * a.H * a.maps + (g * rh + (uint32_t)r % rh) * a.maps + m;
+#pragma unroll
+        for (int i = 0; i < CI; i++) {
+            const uint32_t c = tid + kCfThreads * i;
+            if (c >= a.dv) continue;
+            if (splits == 1) a.dst[item * a.dv + c] = acc[r][i] * Al[r];
+            else part[(item * splits + blockIdx.y) * (4 + a.dv) + 4 + c] = acc[r][i];
+        }
+    }
+}
+static size_t cf_smem(uint32_t dk, uint32_t dv, bool alias) {
+    return ((size_t)kCfRows * dk + (size_t)kCfKeys * (dk + 4) + kCfRows * kCfKeys + kCfRows + (alias ? 0 : (size_t)kCfKeys * dv)) * sizeof(float);
+}
+static bool cf_alias(const ZgSeqOp& s) {   // the value row is the head of the key row (one key head, one map, same cache and column)
+    return s.buf[2] == s.buf[3] && s.off[1] == s.off[2] && s.n[2] == 1 && s.n[3] == 1 && s.n[5] <= s.n[4] && s.n[7] == s.n[8];
+}
 template <int OC>
 static void launch_cached_attention_tiled(const CaArgs& a, uint32_t splits, float* part, cudaStream_t st) {
     constexpr int DV = 16 * OC;
@@ -360,9 +493,17 @@ static void launch_cached_attention_tiled(const CaArgs& a, uint32_t splits, floa
 static bool ca_aligned(const ZgSeqOp& s) {
     return s.n[4] % 4 == 0 && s.n[5] % 4 == 0 && s.n[6] % 4 == 0 && s.n[7] % 4 == 0 && s.n[8] % 4 == 0 && s.off[0] % 4 == 0 && s.off[1] % 4 == 0 && s.off[2] % 4 == 0;
 }
+static bool ca_few(const ZgSeqOp& s) {
+    return ca_aligned(s) && s.n[0] * (s.n[1] / s.n[2]) <= (uint32_t)kCfRows && cf_smem(s.n[4], s.n[5], cf_alias(s)) <= 200 * 1024;
+}
 // key shares per row tile: few CTAs and a long cache (decoding) spread over more of them
 static uint32_t ca_splits(const ZgSeqOp& s) {
     if (!ca_aligned(s)) return 1;
+    if (ca_few(s)) {
+        const uint32_t reach = s.off[3] ? min(s.n[9], s.off[4] + s.n[0]) : s.n[9];
+        const uint32_t S = (reach + kCfKeys - 1) / kCfKeys;
+        return S < 2 ? 1 : (S > (uint32_t)kCtMaxSplits ? (uint32_t)kCtMaxSplits : S);
+    }
     const uint32_t rh = s.n[1] / s.n[2], n_tiles = (s.n[0] * rh + kCtBQ - 1) / kCtBQ, dvs = s.n[5] > 128 ? 256 : 128;
     const uint32_t ctas = n_tiles * s.n[2] * s.n[3] * ((s.n[5] + dvs - 1) / dvs);
     const uint32_t reach = s.off[3] ? min(s.n[9], s.off[4] + s.n[0]) : s.n[9];     // keys a row can see at most
@@ -631,7 +772,24 @@ bool zg_launch_mix_op(const ZgOp& op, float* const* bufs, float* scratch, cudaSt
             a.T = s.n[0]; a.H = s.n[1]; a.G = s.n[2]; a.maps = s.n[3]; a.dk = s.n[4]; a.dv = s.n[5]; a.q_rs = s.n[6]; a.q_off = s.off[0];
             a.kw = s.n[7]; a.k_off = s.off[1]; a.vw = s.n[8]; a.v_off = s.off[2]; a.R = s.n[9]; a.kind = s.off[3]; a.size = s.off[4]; a.scale = s.f[0];
             const bool aligned = ca_aligned(s) && ((reinterpret_cast<uintptr_t>(a.q) | reinterpret_cast<uintptr_t>(a.kc) | reinterpret_cast<uintptr_t>(a.vc)) & 15) == 0;
-            if (aligned) {
+            if (aligned && ca_few(s)) {
+                const uint32_t S = scratch ? ca_splits(s) : 1, alias = cf_alias(s) ? 1u : 0u;
+                float* part = S > 1 ? scratch : nullptr;
+                const size_t smem = cf_smem(a.dk, a.dv, alias != 0);
+                const dim3 grid(a.G * a.maps, S);
+#define ZG_CF(CI_)                                                                                                                         \
+    do {                                                                                                                                   \
+        static size_t most = 48 * 1024;                                                                                                    \
+        if (smem > most) { cudaFuncSetAttribute(k_cached_attention_few<CI_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); most = smem; } \
+        launch_pdl(k_cached_attention_few<CI_>, grid, dim3(kCfThreads), smem, st, a, a.H / a.G, S, part, alias);                            \
+    } while (0)
+                if (a.dv <= 256) ZG_CF(1); else if (a.dv <= 512) ZG_CF(2); else ZG_CF(4);
+#undef ZG_CF
+                if (S > 1) {
+                    ZG_SEQ_CHECK();
+                    launch_pdl(k_cached_attention_merge, dim3(a.T * a.H * a.maps, (a.dv + 127) / 128), dim3(128), 0, st, a.dst, (const float*)part, a.dv, S);
+                }
+            } else if (aligned) {
                 const uint32_t S = scratch ? ca_splits(s) : 1;
                 float* part = S > 1 ? scratch : nullptr;
                 if (a.dv > 128) launch_cached_attention_tiled<16>(a, S, part, st);
