@@ -179,9 +179,13 @@ __global__ void __launch_bounds__(kCtThreads) k_cached_attention_tiled(CaArgs a,
     pdl_enter();
     constexpr int DV = 16 * OC, KP = kCtDS + 4, PP = kCtBK + 4;
     extern __shared__ __align__(16) float sm[];
-    float* Qs = sm;                                    // [64][64]
-    float* Ks = Qs + kCtBQ * kCtDS;                    // [64][64 + 4]
-    float* Ps = Ks + kCtBK * KP;                       // [64][64 + 4]
+    // The 64-wide slices of the queries and keys are double-buffered: while a slice is multiplied, cp.async brings the next
+    // one (of this key tile or the first of the next), so the cache's latency hides behind the arithmetic.  Queries no wider
+    // than one slice are loaded once and keep a single buffer.
+    const bool q_once = a.dk <= (uint32_t)kCtDS;
+    float* Qs = sm;                                    // [1 or 2][64][64]
+    float* Ks = Qs + (q_once ? 1 : 2) * kCtBQ * kCtDS; // [2][64][64 + 4]
+    float* Ps = Ks + 2 * kCtBK * KP;                   // [64][64 + 4]
     float* Vs = Ps + kCtBQ * PP;                       // [64][DV]
     const uint32_t tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
     const uint32_t n_vs = (a.dv + DV - 1) / DV;
@@ -205,17 +209,34 @@ __global__ void __launch_bounds__(kCtThreads) k_cached_attention_tiled(CaArgs a,
         p_r[i] = pos0 + (ok_r[i] ? r / rh : 0);
         lo_r[i] = mask_low(p_r[i], a.kind, a.size);
     }
-    auto load_q = [&](uint32_t d0) {
+    // 16 bytes global -> shared without passing through registers; `on` false writes zeros (nothing is read)
+    auto copy16 = [](float* dst, const float* src, bool on) {
+        const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+        const int n = on ? 16 : 0;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(n) : "memory");
+    };
+    auto load_q = [&](uint32_t d0, uint32_t stage) {
         for (uint32_t i = tid; i < kCtBQ * (kCtDS / 4); i += kCtThreads) {
             const uint32_t rr = i / (kCtDS / 4), c4 = i % (kCtDS / 4), r = r0 + rr;
-            float4 val = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (r < total && d0 + 4 * c4 < a.dk)
-                val = *reinterpret_cast<const float4*>(a.q + (size_t)(r / rh) * a.q_rs + a.q_off + (size_t)((g * rh + r % rh) * a.maps + m) * a.dk + d0 + 4 * c4);
-            *reinterpret_cast<float4*>(Qs + rr * kCtDS + 4 * c4) = val;
+            const bool on = r < total && d0 + 4 * c4 < a.dk;
+            const float* src = on ? a.q + (size_t)(r / rh) * a.q_rs + a.q_off + (size_t)((g * rh + r % rh) * a.maps + m) * a.dk + d0 + 4 * c4 : a.q;
+            copy16(Qs + stage * kCtBQ * kCtDS + rr * kCtDS + 4 * c4, src, on);
         }
     };
-    const bool q_once = a.dk <= (uint32_t)kCtDS;
-    if (q_once) load_q(0);
+    auto load_k = [&](uint32_t s0, uint32_t d0, uint32_t stage) {
+        for (uint32_t i = tid; i < kCtBK * (kCtDS / 4); i += kCtThreads) {
+            const uint32_t rr = i / (kCtDS / 4), c4 = i % (kCtDS / 4);
+            const bool on = s0 + rr < k_end && d0 + 4 * c4 < a.dk;
+            copy16(Ks + stage * kCtBK * KP + rr * KP + 4 * c4, on ? kbase + (size_t)((s0 + rr) % a.R) * a.kw + d0 + 4 * c4 : kbase, on);
+        }
+    };
+    auto load_v = [&](uint32_t s0) {
+        for (uint32_t i = tid; i < kCtBK * (DV / 4); i += kCtThreads) {
+            const uint32_t rr = i / (DV / 4), c4 = i % (DV / 4);
+            const bool on = s0 + rr < k_end && 4 * c4 < v_cols;
+            copy16(Vs + rr * DV + 4 * c4, on ? vbase + (size_t)((s0 + rr) % a.R) * a.vw + 4 * c4 : vbase, on);
+        }
+    };
     float o[4][OC], m_run[4], l_run[4];
 #pragma unroll
     for (int r = 0; r < 4; r++) {
@@ -223,38 +244,43 @@ __global__ void __launch_bounds__(kCtThreads) k_cached_attention_tiled(CaArgs a,
 #pragma unroll
         for (int c = 0; c < OC; c++) o[r][c] = 0.0f;
     }
+    const uint32_t n_slices = (a.dk + kCtDS - 1) / kCtDS;
+    uint32_t it = 0;                                   // slices done so far, over all key tiles: slice `it` sits in stage it & 1
+    if (k_begin < k_end) {                             // the first slice of the first tile
+        load_q(0, 0);
+        load_k(k_begin, 0, 0);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
     for (uint32_t s0 = k_begin; s0 < k_end; s0 += kCtBK) {
         float sc[4][4];
 #pragma unroll
         for (int r = 0; r < 4; r++)
 #pragma unroll
             for (int c = 0; c < 4; c++) sc[r][c] = 0.0f;
-        for (uint32_t d0 = 0; d0 < a.dk; d0 += kCtDS) {
-            __syncthreads();                           // the previous slice's (or tile's) readers of Qs / Ks / Ps / Vs are done
-            if (!q_once) load_q(d0);
-            for (uint32_t i = tid; i < kCtBK * (kCtDS / 4); i += kCtThreads) {
-                const uint32_t rr = i / (kCtDS / 4), c4 = i % (kCtDS / 4);
-                float4 val = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (s0 + rr < k_end && d0 + 4 * c4 < a.dk) val = *reinterpret_cast<const float4*>(kbase + (size_t)((s0 + rr) % a.R) * a.kw + d0 + 4 * c4);
-                *reinterpret_cast<float4*>(Ks + rr * KP + 4 * c4) = val;
+        for (uint32_t sl = 0; sl < n_slices; sl++, it++) {
+            const uint32_t d0 = sl * kCtDS, stage = it & 1;
+            __syncthreads();                           // the readers of the other stage (the slice before), of Ps and of Vs (the tile before) are done
+            if (sl + 1 < n_slices) {                   // bring the next slice while this one is multiplied
+                load_q(d0 + kCtDS, stage ^ 1);
+                load_k(s0, d0 + kCtDS, stage ^ 1);
+            } else if (s0 + kCtBK < k_end) {
+                if (!q_once) load_q(0, stage ^ 1);
+                load_k(s0 + kCtBK, 0, stage ^ 1);
             }
-            if (d0 == 0) {
-                for (uint32_t i = tid; i < kCtBK * (DV / 4); i += kCtThreads) {
-                    const uint32_t rr = i / (DV / 4), c4 = i % (DV / 4);
-                    float4 val = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (s0 + rr < k_end && 4 * c4 < v_cols) val = *reinterpret_cast<const float4*>(vbase + (size_t)((s0 + rr) % a.R) * a.vw + 4 * c4);
-                    *reinterpret_cast<float4*>(Vs + rr * DV + 4 * c4) = val;
-                }
-            }
+            if (sl == 0) load_v(s0);                   // needed only after the tile's last slice
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            asm volatile("cp.async.wait_group 1;" ::: "memory");   // everything but the group just committed has landed: this slice is there
             __syncthreads();
+            const float* Qc = Qs + (q_once ? 0 : stage) * kCtBQ * kCtDS;
+            const float* Kc = Ks + stage * kCtBK * KP;
             const uint32_t dn = min((uint32_t)kCtDS, a.dk - d0);
 #pragma unroll 2
             for (uint32_t d = 0; d < dn; d += 4) {
                 float4 qa[4], ka[4];
 #pragma unroll
-                for (int r = 0; r < 4; r++) qa[r] = *reinterpret_cast<const float4*>(Qs + (4 * ty + r) * kCtDS + d);
+                for (int r = 0; r < 4; r++) qa[r] = *reinterpret_cast<const float4*>(Qc + (4 * ty + r) * kCtDS + d);
 #pragma unroll
-                for (int c = 0; c < 4; c++) ka[c] = *reinterpret_cast<const float4*>(Ks + (tx + 16 * c) * KP + d);
+                for (int c = 0; c < 4; c++) ka[c] = *reinterpret_cast<const float4*>(Kc + (tx + 16 * c) * KP + d);
 #pragma unroll
                 for (int r = 0; r < 4; r++)
 #pragma unroll
@@ -263,6 +289,9 @@ __global__ void __launch_bounds__(kCtThreads) k_cached_attention_tiled(CaArgs a,
                         sc[r][c] = fmaf(qa[r].z, ka[c].z, sc[r][c]); sc[r][c] = fmaf(qa[r].w, ka[c].w, sc[r][c]);
                     }
             }
+        }
+        if (n_slices == 1) {                           // the values came with this very slice's group: wait for them too
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
 #pragma unroll
         for (int r = 0; r < 4; r++) {
@@ -484,9 +513,9 @@ static bool cf_alias(const ZgSeqOp& s) {   // the value row is the head of the k
 template <int OC>
 static void launch_cached_attention_tiled(const CaArgs& a, uint32_t splits, float* part, cudaStream_t st) {
     constexpr int DV = 16 * OC;
-    const size_t smem = ((size_t)kCtBQ * kCtDS + (size_t)kCtBK * (kCtDS + 4) + (size_t)kCtBQ * (kCtBK + 4) + (size_t)kCtBK * DV) * sizeof(float);
-    static bool once = false;
-    if (!once) { cudaFuncSetAttribute(k_cached_attention_tiled<OC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); once = true; }
+    const size_t smem = ((size_t)(a.dk <= (uint32_t)kCtDS ? 1 : 2) * kCtBQ * kCtDS + (size_t)2 * kCtBK * (kCtDS + 4) + (size_t)kCtBQ * (kCtBK + 4) + (size_t)kCtBK * DV) * sizeof(float);
+    static size_t most = 0;
+    if (smem > most) { cudaFuncSetAttribute(k_cached_attention_tiled<OC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); most = smem; }
     const uint32_t rh = a.H / a.G, n_tiles = (a.T * rh + kCtBQ - 1) / kCtBQ, n_vs = (a.dv + DV - 1) / DV;
     launch_pdl(k_cached_attention_tiled<OC>, dim3(n_tiles, a.G * a.maps * n_vs, splits), dim3(kCtThreads), smem, st, a, rh, n_tiles, splits, part);
 }
