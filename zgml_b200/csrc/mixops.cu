@@ -174,6 +174,12 @@ __global__ void k_cached_attention(CaArgs a) {
 // unnormalised output) per row for k_cached_attention_merge; a range may be shorter than a tile (its other keys are neither
 // loaded nor counted), since what bounds such a step is how many SMs pull on the cache, not the arithmetic.
 constexpr int kCtBQ = 64, kCtBK = 64, kCtDS = 64, kCtThreads = 256, kCtMaxSplits = 64, kCtMinShare = 32;
+// 16 bytes global -> shared without passing through registers; `on` false writes zeros (nothing is read)
+__device__ __forceinline__ void copy16(float* dst, const float* src, bool on) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    const int n = on ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(n) : "memory");
+}
 template <int OC>
 __global__ void __launch_bounds__(kCtThreads) k_cached_attention_tiled(CaArgs a, uint32_t rh, uint32_t n_tiles, uint32_t splits, float* __restrict__ part) {
     pdl_enter();
@@ -209,12 +215,6 @@ __global__ void __launch_bounds__(kCtThreads) k_cached_attention_tiled(CaArgs a,
         p_r[i] = pos0 + (ok_r[i] ? r / rh : 0);
         lo_r[i] = mask_low(p_r[i], a.kind, a.size);
     }
-    // 16 bytes global -> shared without passing through registers; `on` false writes zeros (nothing is read)
-    auto copy16 = [](float* dst, const float* src, bool on) {
-        const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
-        const int n = on ? 16 : 0;
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(n) : "memory");
-    };
     auto load_q = [&](uint32_t d0, uint32_t stage) {
         for (uint32_t i = tid; i < kCtBQ * (kCtDS / 4); i += kCtThreads) {
             const uint32_t rr = i / (kCtDS / 4), c4 = i % (kCtDS / 4), r = r0 + rr;
@@ -380,22 +380,26 @@ __global__ void __launch_bounds__(128) k_cached_attention_merge(float* __restric
 
 // Few query rows (decoding: tokens x heads of a key group <= 16): what bounds the step is the latency of pulling the cache,
 // so a CTA takes one share of the keys, 32 at a time with WHOLE rows in shared memory — one round of loads per 32 keys instead
-// of one per 64-wide slice — and the shares are merged afterwards.  Thread (row, kq) of 16 x 16 scores keys kq and kq + 16
-// of its row; the 16 threads of a row keep the row's running (max, sum) in step through half-warp shuffles; for the weighted
-// sum thread t owns value columns t + 256 i of all rows.  Where the value row is the head of the key row itself (a latent that
-// serves as both), it is not loaded twice.
-constexpr int kCfRows = 16, kCfKeys = 32, kCfThreads = 256;
+// of one per 64-wide slice — and the shares are merged afterwards.  Scores: the 16 x 32 (row, key) pairs are covered by 32
+// threads holding 4 x 4 pairs each (rows rg + 4 r, keys kg + 8 c: conflict-free 16-byte reads of padded rows), and the eight
+// warps split the key dimension; their partial dot products meet in shared memory.  Then thread (row, kq) of 16 x 16 owns
+// keys kq and kq + 16 of its row, and the 16 threads of a row keep the row's running (max, sum) in step through half-warp
+// shuffles; for the weighted sum thread t owns value columns t + 256 i of all rows.  Where the value row is the head of the
+// key row itself (a latent that serves as both), it is not loaded twice.
+constexpr int kCfRows = 16, kCfKeys = 32, kCfThreads = 256, kCfParts = kCfThreads / 32;
 template <int CI>
 __global__ void __launch_bounds__(kCfThreads) k_cached_attention_few(CaArgs a, uint32_t rh, uint32_t splits, float* __restrict__ part, uint32_t alias) {
     pdl_enter();
     extern __shared__ __align__(16) float sm[];
     const uint32_t KP = a.dk + 4, VP = alias ? KP : a.dv;
-    float* Qs = sm;                                    // [16][dk]
-    float* Ks = Qs + kCfRows * a.dk;                   // [32][dk + 4]
-    float* Ss = Ks + kCfKeys * KP;                     // [16][32] scores, then probabilities
+    float* Qs = sm;                                    // [16][dk + 4]
+    float* Ks = Qs + kCfRows * KP;                     // [32][dk + 4]
+    float* Sp = Ks + kCfKeys * KP;                     // [8][16][32] partial scores of the eight slices of the key dimension
+    float* Ss = Sp + kCfParts * kCfRows * kCfKeys;     // [16][32] probabilities
     float* Al = Ss + kCfRows * kCfKeys;                // [16] rescale of the running sums (at the end: 1 / sum)
     float* Vs = alias ? Ks : Al + kCfRows;             // [32][dv]
     const uint32_t tid = threadIdx.x, row = tid >> 4, kq = tid & 15;
+    const uint32_t warp = tid >> 5, rg = (tid & 31) >> 3, kg = tid & 7;
     const uint32_t gm = blockIdx.x, g = gm / a.maps, m = gm % a.maps;
     const uint32_t pos0 = (uint32_t)ctl_word(a.ctl, ZG_CTL_POS), slot = (uint32_t)ctl_word(a.ctl, ZG_CTL_SLOT);
     const uint32_t total = a.T * rh, p_max = pos0 + a.T - 1;
@@ -407,10 +411,10 @@ __global__ void __launch_bounds__(kCfThreads) k_cached_attention_few(CaArgs a, u
     const bool ok = row < total;
     const uint32_t p_r = pos0 + (ok ? row / rh : 0), lo_r = mask_low(p_r, a.kind, a.size);
     const uint32_t dk4 = a.dk / 4, dv4 = a.dv / 4;
-    for (uint32_t i = tid; i < total * dk4; i += kCfThreads) {
+    const uint32_t chunk4 = (dk4 + kCfParts - 1) / kCfParts, d_begin = 4 * min(dk4, warp * chunk4), d_end = 4 * min(dk4, (warp + 1) * chunk4);
+    for (uint32_t i = tid; i < kCfRows * dk4; i += kCfThreads) {     // rows past the step's are zero: their scores are never used
         const uint32_t r = i / dk4, c4 = i % dk4;
-        *reinterpret_cast<float4*>(Qs + r * a.dk + 4 * c4) =
-            *reinterpret_cast<const float4*>(a.q + (size_t)(r / rh) * a.q_rs + a.q_off + (size_t)((g * rh + r % rh) * a.maps + m) * a.dk + 4 * c4);
+        copy16(Qs + r * KP + 4 * c4, r < total ? a.q + (size_t)(r / rh) * a.q_rs + a.q_off + (size_t)((g * rh + r % rh) * a.maps + m) * a.dk + 4 * c4 : a.q, r < total);
     }
     float acc[kCfRows][CI];
 #pragma unroll
@@ -421,32 +425,52 @@ __global__ void __launch_bounds__(kCfThreads) k_cached_attention_few(CaArgs a, u
     for (uint32_t s0 = k_begin; s0 < k_end; s0 += kCfKeys) {
         const uint32_t nk = min((uint32_t)kCfKeys, k_end - s0);
         __syncthreads();                               // the previous keys' readers are done
-        for (uint32_t i = tid; i < nk * dk4; i += kCfThreads) {
+        for (uint32_t i = tid; i < kCfKeys * dk4; i += kCfThreads) {
             const uint32_t kk = i / dk4, c4 = i % dk4;
-            *reinterpret_cast<float4*>(Ks + kk * KP + 4 * c4) = *reinterpret_cast<const float4*>(kbase + (size_t)((s0 + kk) % a.R) * a.kw + 4 * c4);
+            copy16(Ks + kk * KP + 4 * c4, kk < nk ? kbase + (size_t)((s0 + kk) % a.R) * a.kw + 4 * c4 : kbase, kk < nk);
         }
         if (!alias)
             for (uint32_t i = tid; i < nk * dv4; i += kCfThreads) {
                 const uint32_t kk = i / dv4, c4 = i % dv4;
-                *reinterpret_cast<float4*>(Vs + kk * VP + 4 * c4) = *reinterpret_cast<const float4*>(vbase + (size_t)((s0 + kk) % a.R) * a.vw + 4 * c4);
+                copy16(Vs + kk * VP + 4 * c4, vbase + (size_t)((s0 + kk) % a.R) * a.vw + 4 * c4, true);
             }
+        asm volatile("cp.async.commit_group;" ::: "memory");   // every load of the share is in flight at once: one round trip
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+        {
+            float sc[4][4];
+#pragma unroll
+            for (int r = 0; r < 4; r++)
+#pragma unroll
+                for (int c = 0; c < 4; c++) sc[r][c] = 0.0f;
+            for (uint32_t d = d_begin; d < d_end; d += 4) {
+                float4 qa[4], ka[4];
+#pragma unroll
+                for (int r = 0; r < 4; r++) qa[r] = *reinterpret_cast<const float4*>(Qs + (rg + 4 * r) * KP + d);
+#pragma unroll
+                for (int c = 0; c < 4; c++) ka[c] = *reinterpret_cast<const float4*>(Ks + (kg + 8 * c) * KP + d);
+#pragma unroll
+                for (int r = 0; r < 4; r++)
+#pragma unroll
+                    for (int c = 0; c < 4; c++) {
+                        sc[r][c] = fmaf(qa[r].x, ka[c].x, sc[r][c]); sc[r][c] = fmaf(qa[r].y, ka[c].y, sc[r][c]);
+                        sc[r][c] = fmaf(qa[r].z, ka[c].z, sc[r][c]); sc[r][c] = fmaf(qa[r].w, ka[c].w, sc[r][c]);
+                    }
+            }
+#pragma unroll
+            for (int r = 0; r < 4; r++)
+#pragma unroll
+                for (int c = 0; c < 4; c++) Sp[(warp * kCfRows + rg + 4 * r) * kCfKeys + kg + 8 * c] = sc[r][c];
+        }
         __syncthreads();
         float sv[2];
 #pragma unroll
         for (int u = 0; u < 2; u++) {
             const uint32_t kk = kq + 16 * u, j = s0 + kk;
-            sv[u] = -INFINITY;
-            if (ok && kk < nk && j <= p_r && j >= lo_r) {
-                const float* qr = Qs + row * a.dk;
-                const float* kr = Ks + kk * KP;
-                float d0 = 0.0f, d1 = 0.0f;
-                for (uint32_t d = 0; d < a.dk; d += 4) {
-                    const float4 qv = *reinterpret_cast<const float4*>(qr + d), kv = *reinterpret_cast<const float4*>(kr + d);
-                    d0 = fmaf(qv.x, kv.x, fmaf(qv.y, kv.y, d0));
-                    d1 = fmaf(qv.z, kv.z, fmaf(qv.w, kv.w, d1));
-                }
-                sv[u] = (d0 + d1) * a.scale;
-            }
+            float d = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kCfParts; w++) d += Sp[(w * kCfRows + row) * kCfKeys + kk];
+            sv[u] = (ok && kk < nk && j <= p_r && j >= lo_r) ? d * a.scale : -INFINITY;
         }
         float rmax = fmaxf(sv[0], sv[1]);
 #pragma unroll
@@ -472,15 +496,18 @@ __global__ void __launch_bounds__(kCfThreads) k_cached_attention_few(CaArgs a, u
 #pragma unroll
             for (int i = 0; i < CI; i++) acc[r][i] *= al;
         }
-        for (uint32_t kk = 0; kk < nk; kk++) {
-            float v[CI];
+        for (uint32_t kk = 0; kk < nk; kk += 4) {      // four keys per trip: the probabilities are read as float4s
+            float v[4][CI];
 #pragma unroll
-            for (int i = 0; i < CI; i++) { const uint32_t c = tid + kCfThreads * i; v[i] = c < a.dv ? Vs[kk * VP + c] : 0.0f; }
+            for (int u = 0; u < 4; u++)
+#pragma unroll
+                for (int i = 0; i < CI; i++) { const uint32_t c = tid + kCfThreads * i; v[u][i] = (c < a.dv && kk + u < nk) ? Vs[(kk + u) * VP + c] : 0.0f; }
 #pragma unroll
             for (int r = 0; r < kCfRows; r++) {
-                const float pr = Ss[r * kCfKeys + kk];
+                const float4 pr = *reinterpret_cast<const float4*>(Ss + r * kCfKeys + kk);
 #pragma unroll
-                for (int i = 0; i < CI; i++) acc[r][i] = fmaf(pr, v[i], acc[r][i]);
+                for (int i = 0; i < CI; i++)
+                    acc[r][i] = fmaf(pr.x, v[0][i], fmaf(pr.y, v[1][i], fmaf(pr.z, v[2][i], fmaf(pr.w, v[3][i], acc[r][i]))));
             }
         }
     }
@@ -505,7 +532,7 @@ __global__ void __launch_bounds__(kCfThreads) k_cached_attention_few(CaArgs a, u
     }
 }
 static size_t cf_smem(uint32_t dk, uint32_t dv, bool alias) {
-    return ((size_t)kCfRows * dk + (size_t)kCfKeys * (dk + 4) + kCfRows * kCfKeys + kCfRows + (alias ? 0 : (size_t)kCfKeys * dv)) * sizeof(float);
+    return ((size_t)(kCfRows + kCfKeys) * (dk + 4) + (size_t)(kCfParts + 1) * kCfRows * kCfKeys + kCfRows + (alias ? 0 : (size_t)kCfKeys * dv)) * sizeof(float);
 }
 static bool cf_alias(const ZgSeqOp& s) {   // the value row is the head of the key row (one key head, one map, same cache and column)
     return s.buf[2] == s.buf[3] && s.off[1] == s.off[2] && s.n[2] == 1 && s.n[3] == 1 && s.n[5] <= s.n[4] && s.n[7] == s.n[8];
