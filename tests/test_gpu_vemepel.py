@@ -262,9 +262,10 @@ def test_far_key_among_hundreds(cuda_backend, layer):
     close(s)
 
 
-@pytest.mark.parametrize("layer", [latent_layer(heads=4, dim=12, vdim=8, kv_rank=320), latent2_layer(heads=3, dim=72, rot_dim=8, vdim=20, kv_rank=136),
+@pytest.mark.parametrize("layer", [latent_layer(heads=4, dim=12, vdim=8, kv_rank=320), latent_layer(heads=2, dim=8, vdim=8, kv_rank=520),
+                                   latent2_layer(heads=3, dim=72, rot_dim=8, vdim=20, kv_rank=136),
                                    diff_layer(heads=4, kv_heads=2, dim=68, vdim=132, block=290), diff_layer(heads=8, kv_heads=1, dim=4, vdim=4, block=129)],
-                         ids=["latent-rank320", "latent2-dim72", "diff-wide", "diff-8-per-group"])
+                         ids=["latent-rank320", "latent-rank520", "latent2-dim72", "diff-wide", "diff-8-per-group"])
 def test_wide_heads_and_split_decoding(cuda_backend, layer):
     """Key and value sizes beyond one 64-wide slice of the tiled kernel (several key slices, two value slices) and caches long
     enough that single-token steps deal their keys to several CTAs and merge the shares."""

@@ -560,7 +560,7 @@ static uint32_t ca_splits(const ZgSeqOp& s) {
         const uint32_t S = (reach + kCfKeys - 1) / kCfKeys;
         return S < 2 ? 1 : (S > (uint32_t)kCtMaxSplits ? (uint32_t)kCtMaxSplits : S);
     }
-    const uint32_t rh = s.n[1] / s.n[2], n_tiles = (s.n[0] * rh + kCtBQ - 1) / kCtBQ, dvs = s.n[5] > 128 ? 256 : 128;
+    const uint32_t rh = s.n[1] / s.n[2], n_tiles = (s.n[0] * rh + kCtBQ - 1) / kCtBQ, dvs = s.n[5] > 256 ? 512 : (s.n[5] > 128 ? 256 : 128);
     const uint32_t ctas = n_tiles * s.n[2] * s.n[3] * ((s.n[5] + dvs - 1) / dvs);
     const uint32_t reach = s.off[3] ? min(s.n[9], s.off[4] + s.n[0]) : s.n[9];     // keys a row can see at most
     uint32_t S = 160 / (ctas ? ctas : 1), most = reach / kCtMinShare;
@@ -600,8 +600,9 @@ __device__ __forceinline__ float hl_gated(const HlArgs& a, float v, uint32_t m, 
     return a.gate ? v * sigmoidf_(a.gate[(size_t)m * a.gate_rs + (h * a.N + n) / a.gate_group]) : v;
 }
 constexpr int kHlRows = 8;
-// few rows: one warp per (head, output), the weight row streamed once for all rows
-template <typename WT>
+// few rows: one warp per (head, output), the weight row streamed once for all rows; 16-byte weight loads (VEC) when the rows
+// and the head's slices of the input start on 16-byte boundaries and K is a whole number of them
+template <typename WT, bool VEC>
 __global__ void k_head_linear_rows(HlArgs a, const WT* __restrict__ W) {
     pdl_enter();
     const uint32_t n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31, h = blockIdx.y;
@@ -611,11 +612,30 @@ __global__ void k_head_linear_rows(HlArgs a, const WT* __restrict__ W) {
     float acc[kHlRows];
 #pragma unroll
     for (int m = 0; m < kHlRows; m++) acc[m] = 0.0f;
-    for (uint32_t k = lane; k < a.K; k += 32) {
-        const float wv = wld(w, k);
+    if (VEC) {
+        constexpr int V = WVec<WT>::n;
+        for (uint32_t k = lane * V; k < a.K; k += 32 * V) {
+            float wv[V];
+            wld_vec<WT>(w + k, wv);
 #pragma unroll
-        for (int m = 0; m < kHlRows; m++)
-            if (m < (int)a.T) acc[m] = fmaf(x[(size_t)m * a.src_rs + k], wv, acc[m]);
+            for (int m = 0; m < kHlRows; m++) {
+                if (m < (int)a.T) {
+                    const float4* xv = reinterpret_cast<const float4*>(x + (size_t)m * a.src_rs + k);
+#pragma unroll
+                    for (int i = 0; i < V / 4; i++) {
+                        const float4 q = xv[i];
+                        acc[m] = fmaf(q.x, wv[4 * i], fmaf(q.y, wv[4 * i + 1], fmaf(q.z, wv[4 * i + 2], fmaf(q.w, wv[4 * i + 3], acc[m]))));
+                    }
+                }
+            }
+        }
+    } else {
+        for (uint32_t k = lane; k < a.K; k += 32) {
+            const float wv = wld(w, k);
+#pragma unroll
+            for (int m = 0; m < kHlRows; m++)
+                if (m < (int)a.T) acc[m] = fmaf(x[(size_t)m * a.src_rs + k], wv, acc[m]);
+        }
     }
 #pragma unroll
     for (int m = 0; m < kHlRows; m++) {
@@ -848,7 +868,8 @@ bool zg_launch_mix_op(const ZgOp& op, float* const* bufs, float* scratch, cudaSt
             } else if (aligned) {
                 const uint32_t S = scratch ? ca_splits(s) : 1;
                 float* part = S > 1 ? scratch : nullptr;
-                if (a.dv > 128) launch_cached_attention_tiled<16>(a, S, part, st);
+                if (a.dv > 256) launch_cached_attention_tiled<32>(a, S, part, st);   // a latent of rank <= 512 in one slice: its scores are taken once
+                else if (a.dv > 128) launch_cached_attention_tiled<16>(a, S, part, st);
                 else switch ((a.dv + 15) / 16) {
                     case 1: launch_cached_attention_tiled<1>(a, S, part, st); break;
                     case 2: launch_cached_attention_tiled<2>(a, S, part, st); break;
@@ -884,7 +905,10 @@ bool zg_launch_mix_op(const ZgOp& op, float* const* bufs, float* scratch, cudaSt
             a.gate = s.buf[3] != ZG_NO_BUF ? bufs[s.buf[3]] + s.off[3] : nullptr; a.gate_rs = s.off[4]; a.gate_group = s.n[9];
             ZG_SEQ_WDT(s.n[8], {
                 const WT* W = wptr<WT>(bufs, s.buf[2], s.off[0]);
-                if (a.T <= (uint32_t)kHlRows) launch_pdl(k_head_linear_rows<WT>, dim3((a.N + 7) / 8, a.H), dim3(256), 0, st, a, W);
+                constexpr uint32_t V = WVec<WT>::n;
+                const bool vec = a.K % V == 0 && a.src_hs % 4 == 0 && a.src_rs % 4 == 0 && ((reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(a.src)) & 15) == 0;
+                if (a.T <= (uint32_t)kHlRows && vec) launch_pdl(k_head_linear_rows<WT, true>, dim3((a.N + 7) / 8, a.H), dim3(256), 0, st, a, W);
+                else if (a.T <= (uint32_t)kHlRows) launch_pdl(k_head_linear_rows<WT, false>, dim3((a.N + 7) / 8, a.H), dim3(256), 0, st, a, W);
                 else k_head_linear_tile<WT><<<dim3((a.N + kHlTN - 1) / kHlTN, (a.T + kHlTM - 1) / kHlTM, a.H), 256, 0, st>>>(a, W);
             });
             ZG_SEQ_CHECK();
