@@ -868,7 +868,12 @@ bool zg_launch_mix_op(const ZgOp& op, float* const* bufs, float* scratch, cudaSt
             } else if (aligned) {
                 const uint32_t S = scratch ? ca_splits(s) : 1;
                 float* part = S > 1 ? scratch : nullptr;
-                if (a.dv > 256) launch_cached_attention_tiled<32>(a, S, part, st);   // a latent of rank <= 512 in one slice: its scores are taken once
+                // A latent of rank <= 512 in ONE value slice takes its scores once instead of once per 256 columns, but halves the
+                // number of CTAs: worth it only while they still fill the GPU one and a half times.
+                static int n_sm = 0;
+                if (!n_sm) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev); if (n_sm <= 0) n_sm = 1; }
+                const uint32_t row_ctas = ((a.T * (a.H / a.G) + kCtBQ - 1) / kCtBQ) * a.G * a.maps * S * ((a.dv + 511) / 512);
+                if (a.dv > 256 && 2 * row_ctas >= 3 * (uint32_t)n_sm) launch_cached_attention_tiled<32>(a, S, part, st);
                 else if (a.dv > 128) launch_cached_attention_tiled<16>(a, S, part, st);
                 else switch ((a.dv + 15) / 16) {
                     case 1: launch_cached_attention_tiled<1>(a, S, part, st); break;
