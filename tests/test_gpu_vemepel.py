@@ -329,6 +329,21 @@ def test_wider_model(cuda_backend, dtype):
     close(s)
 
 
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_odd_sizes(cuda_backend, dtype):
+    """Nothing is a multiple of 4: the unaligned forms of every kernel (scalar loads, one warp per query, exact matmuls)."""
+    cfg = config([diff_layer(heads=3, kv_heads=1, dim=5, vdim=7, block=9, mlp=moe(experts=3, top=2, ff=11)),
+                  latent2_layer(heads=3, dim=5, rot_dim=6, vdim=7, kv_rank=9, mlp=dense(ff=13)),
+                  latent_layer(heads=2, dim=7, vdim=3, kv_rank=11), diff_layer(heads=3, kv_heads=1, dim=5, vdim=7, kv_from=0, block=4)], width=37, vocab=53)
+    W = random_weights(cfg, seed=19, qk_gain=2.0)
+    toks = tokens(cfg, 41)
+    want = ref.forward(cfg, as_f64(W), toks)
+    s = open_model(cuda_backend, cfg, W, dtype, max_chunk=32)
+    got = np.concatenate([s.feed("a", toks[:35], range(35))] + [s.feed("a", [t], [0]) for t in toks[35:]])
+    assert rel(got, want) < tol(dtype)
+    close(s)
+
+
 # ── the entry points ──
 def _write_model(tmp_path, cfg, W):
     from zgml_b200.host.safetensors import write_safetensors
