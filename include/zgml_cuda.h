@@ -52,8 +52,12 @@ typedef enum ZgOpTag {
     ZG_OP_ALLGATHER = 13, /* dst[dst_offset + r * n ..) = rank r's src[src_offset .. + n), every rank */
     /* Sequence-model extensions (no zgml counterpart): the building blocks of decoder stacks that are not LLaMA-shaped —
      * dense 16-bit / f32 weights, affine norms with a fused residual, windowed attention with a sink, short causal
-     * convolutions, a gated delta-rule recurrence, a routed mixture of experts.  All take a ZgSeqOp (below); per-sequence
-     * state (key ring, recurrent state, convolution tail) lives in EXTERNAL buffers shared by the programs of a session,
+     * convolutions, a gated delta-rule recurrence, a routed mixture of experts; and (from TOKEN_SHIFT on) mixers that
+     * attend over a per-sequence cache of keys and values or of one latent that serves as both: token shift, a learned
+     * average over the depth of the stack, rotary positions, the cache append, attention over the cache with grouped heads,
+     * several score maps per head and causal / window / block masks, head-wise products, PolyNorm.  All take a ZgSeqOp
+     * (below); per-sequence state (key ring or cache, recurrent state, convolution tail, shifted row) lives in EXTERNAL
+     * buffers shared by the programs of a session,
      * and the run-time position / state slot / token ids are read from a small control buffer, so one CUDA graph serves
      * every step. */
     ZG_OP_EMBED = 14,
